@@ -1,0 +1,127 @@
+/*
+ * b200fa — C ABI of the B200 (sm_100a) flash-attention library.
+ *
+ * This is the native boundary behind aten::_scaled_dot_product_flash_attention and
+ * aten::_scaled_dot_product_flash_attention_backward on the `mojo` PyTorch device.  It takes
+ * the place of the reference's CPython bridge functions, which receive raw device addresses,
+ * sizes and a scale as positional integers/floats:
+ *   forward : torch_mojo_backend/eager_flash_attention/fa4_ops.mojo:61-102 (dense),
+ *             :428-449 (strided q/k/v), :666-744 (BHSD)
+ *   backward: torch_mojo_backend/eager_flash_attention/fa4_ops.mojo:158-226
+ *   call sites: torch_mojo_backend/eager_kernels/aten_fast.py:7216-7281 and :7325-7399
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE address (except `status_word`, also a device address, and the
+ *     descriptor structs themselves, which are host memory).
+ *   - Tensors are described in logical (B, H, S, D) order with strides in ELEMENTS, so dense
+ *     BHSD tensors, BTHD-stored transposed views and fused-QKV gapped views all go through
+ *     the same entry point without a copy.  The D stride must be 1.
+ *   - The library never allocates or frees device memory and never synchronises; work is
+ *     enqueued on `stream` (a cudaStream_t; NULL = the legacy default stream).
+ *   - All arguments are validated before anything is launched.  Functions return 0 on
+ *     success or a negative B200FA_ERR_* code; no C++ exception crosses this boundary.
+ *   - `status_word` (optional, may be NULL) points to a zero-initialised uint32 in device
+ *     memory.  A kernel whose internal wait exceeded its budget writes a non-zero code there
+ *     and finishes early instead of hanging; the caller reads it after synchronising.
+ */
+#ifndef B200FA_H_
+#define B200FA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200FA_VERSION 1
+
+/* element types */
+#define B200FA_F32 0
+#define B200FA_BF16 1
+#define B200FA_F16 2
+
+/* error codes */
+#define B200FA_OK 0
+#define B200FA_ERR_BAD_DTYPE (-1)
+#define B200FA_ERR_BAD_SHAPE (-2)
+#define B200FA_ERR_BAD_STRIDE (-3)
+#define B200FA_ERR_MISALIGNED (-4)
+#define B200FA_ERR_WORKSPACE (-5)
+#define B200FA_ERR_UNSUPPORTED (-6)
+#define B200FA_ERR_CUDA (-7)
+#define B200FA_ERR_NULL (-8)
+#define B200FA_ERR_TIMEOUT (-9)
+
+/* A 4-D tensor view in logical (batch, head, sequence, head_dim) order; strides in elements. */
+typedef struct b200fa_tensor4 {
+  void* ptr;
+  int64_t shape[4];
+  int64_t stride[4];
+} b200fa_tensor4;
+
+/*
+ * Forward: out = softmax(scale * q k^T [+ causal mask]) v,  lse = logsumexp of the scaled,
+ * masked scores (natural log), fp32, contiguous (B, Hq, Sq).
+ *   q, out : (B, Hq, Sq, D);  k, v : (B, Hkv, Sk, D) with Hq % Hkv == 0 (query head h reads
+ *   key/value head h / (Hq / Hkv));  Sq == Sk;  D in {64, 128}.
+ *   dtype  : B200FA_BF16 / B200FA_F16 run the tcgen05 tensor-core kernel,
+ *            B200FA_F32 runs an exact-fp32 SIMT kernel.
+ * Replaces flash_attention_fwd_<dtype>_d<D>_causal{,_strided_qkv,_bhsd}
+ * (torch_mojo_backend/eager_flash_attention/fa4_ops.mojo:61-102, 428-449, 666-744).
+ */
+int b200fa_fwd(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_tensor4* v,
+               const b200fa_tensor4* out, float* lse, int dtype, int causal, float scale,
+               void* stream, int device, uint32_t* status_word);
+
+/*
+ * Scratch bytes b200fa_bwd needs for a problem of this size (fp32 dQ accumulator plus the
+ * per-row softmax statistics).  Mirrors the scratch the reference allocates in
+ * torch_mojo_backend/eager_kernels/aten_fast.py:7314-7324.
+ */
+size_t b200fa_bwd_workspace_bytes(int64_t batch, int64_t heads_q, int64_t heads_kv, int64_t seqlen,
+                                  int64_t head_dim, int dtype);
+
+/*
+ * Backward: given dout and the forward's out/lse, writes dq (B,Hq,S,D) and dk, dv (B,Hkv,S,D).
+ * `workspace` is caller-owned device scratch of at least b200fa_bwd_workspace_bytes(...)
+ * bytes, 256-byte aligned; its contents on entry are irrelevant (the library clears what it
+ * needs on `stream`).
+ * Replaces flash_attention_bwd_<dtype>_d<D>_causal{,_strided_qkv}
+ * (torch_mojo_backend/eager_flash_attention/fa4_ops.mojo:158-226).
+ */
+int b200fa_bwd(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_tensor4* v,
+               const b200fa_tensor4* out, const b200fa_tensor4* dout, const float* lse,
+               const b200fa_tensor4* dq, const b200fa_tensor4* dk, const b200fa_tensor4* dv,
+               void* workspace, size_t workspace_bytes, int dtype, int causal, float scale,
+               void* stream, int device, uint32_t* status_word);
+
+/*
+ * Same contracts as b200fa_fwd / b200fa_bwd, but always run the exact-fp32 SIMT kernels
+ * whatever the storage type (16-bit inputs are widened to fp32 on load).  They exist so the
+ * tensor-core kernels can be cross-checked on the device at sizes where a CPU comparison
+ * would take minutes; they have no counterpart in the reference.
+ */
+int b200fa_fwd_simt(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_tensor4* v,
+                    const b200fa_tensor4* out, float* lse, int dtype, int causal, float scale,
+                    void* stream, int device, uint32_t* status_word);
+int b200fa_bwd_simt(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_tensor4* v,
+                    const b200fa_tensor4* out, const b200fa_tensor4* dout, const float* lse,
+                    const b200fa_tensor4* dq, const b200fa_tensor4* dk, const b200fa_tensor4* dv,
+                    void* workspace, size_t workspace_bytes, int dtype, int causal, float scale,
+                    void* stream, int device, uint32_t* status_word);
+
+/* Human-readable text for a B200FA_ERR_* code (static storage). */
+const char* b200fa_strerror(int code);
+
+/* B200FA_VERSION the library was built from. */
+int b200fa_version(void);
+
+/* Number of kernels the library has launched in this process (test/bench accounting; the
+ * reference counts bridge calls the same way, torch_mojo_backend/testing.py:32-136). */
+uint64_t b200fa_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200FA_H_ */

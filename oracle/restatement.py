@@ -1,0 +1,96 @@
+"""TEST INFRASTRUCTURE ONLY — numpy float64 restatement of the reference's attention math.
+
+Parity status: the reference's Mojo kernels cannot be built or run in this environment
+(they need the ``mojo``/``max`` toolchain), and the reference ships no golden vectors, so this
+restatement is NOT pinned against outputs of the reference's own kernels ("parity unpinned"
+in that sense).  It is pinned against the expectation the reference's own GPU tests use —
+torch's CPU fp32 SDPA on seeded inputs (tests/test_eager_kernels.py:9495-9535) and an explicit
+masked ``logsumexp`` (tests/test_eager_kernels.py:9556-9571) — by ``tests/test_oracle.py`` and
+the committed fixtures in ``tests/golden``.
+
+Each function follows the arithmetic of the reference kernel it cites, written tile-free in
+float64 so it is an independent check of torch's CPU SDPA rather than a copy of it.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+
+LOG2E = 1.4426950408889634
+
+
+def expand_kv_heads(x: np.ndarray, heads_q: int) -> np.ndarray:
+    """Query head h reads key/value head h // (Hq // Hkv).
+
+    Follows the head map of torch_mojo_backend/eager_flash_attention/fa4_fwd_kernel.mojo:396-398,428
+    and torch_mojo_backend/aten_functions.py:621-637 (``repeat_interleave`` along the head axis).
+    """
+    group = heads_q // x.shape[1]
+    return np.repeat(x, group, axis=1)
+
+
+def scores(q: np.ndarray, k: np.ndarray, causal: bool) -> np.ndarray:
+    """S = Q K^T with the causal mask ``col > row`` set to -inf.
+
+    Follows torch_mojo_backend/eager_flash_attention/fa4_fwd_kernel.mojo:530-543 (the kernel uses
+    -1e30 for -inf; both give exp2(...) == 0 in float64 and float32 alike).
+    """
+    s = np.einsum("bhqd,bhkd->bhqk", q, k)
+    if causal:
+        sq, sk = s.shape[-2:]
+        mask = np.arange(sk)[None, :] > np.arange(sq)[:, None]
+        s = np.where(mask, -np.inf, s)
+    return s
+
+
+def forward(q, k, v, causal: bool, scale: float):
+    """(out, lse) as the forward kernel defines them.
+
+    Follows torch_mojo_backend/eager_flash_attention/fa4_fwd_kernel.mojo:650-861 (row max, exp2 of
+    ``s*c - m*c`` with ``c = scale*log2(e)``, row sum), :1014-1022 (O / rowsum) and :1138-1160
+    (``LSE = rowmax*c*ln2 + ln(rowsum)``).
+    """
+    q = np.asarray(q, dtype=np.float64)
+    k = expand_kv_heads(np.asarray(k, dtype=np.float64), q.shape[1])
+    v = expand_kv_heads(np.asarray(v, dtype=np.float64), q.shape[1])
+    c = scale * LOG2E
+    s = scores(q, k, causal)
+    m = s.max(axis=-1, keepdims=True)
+    p = np.exp2(s * c - m * c)
+    l = p.sum(axis=-1, keepdims=True)
+    out = np.einsum("bhqk,bhkd->bhqd", p, v) / l
+    lse = (m * c) * np.log(2.0) + np.log(l)
+    return out, lse[..., 0]
+
+
+def backward(q, k, v, dout, causal: bool, scale: float):
+    """(dq, dk, dv) as the backward kernels define them.
+
+    Follows torch_mojo_backend/eager_flash_attention/fa4_bwd_kernel.mojo:1-44 and :810-980:
+    ``dpsum = rowsum(dO*O)`` (preprocess, :1634-1662), ``P = exp2(S*c - lse*log2e)``,
+    ``dV = P^T dO``, ``dP = dO V^T``, ``dS = P*(dP - dpsum)``, ``dK = scale * dS^T Q``
+    (:1443-1444), ``dQ = scale * dS K`` (:1855).  Gradients of shared key/value heads are summed
+    over the query heads of the group.
+    """
+    q = np.asarray(q, dtype=np.float64)
+    heads_q = q.shape[1]
+    heads_kv = np.asarray(k).shape[1]
+    k64 = expand_kv_heads(np.asarray(k, dtype=np.float64), heads_q)
+    v64 = expand_kv_heads(np.asarray(v, dtype=np.float64), heads_q)
+    dout = np.asarray(dout, dtype=np.float64)
+    out, lse = forward(q, k, v, causal, scale)
+    c = scale * LOG2E
+    s = scores(q, k64, causal)
+    p = np.exp2(s * c - (lse * LOG2E)[..., None])
+    dpsum = (dout * out).sum(axis=-1, keepdims=True)
+    dv = np.einsum("bhqk,bhqd->bhkd", p, dout)
+    dp = np.einsum("bhqd,bhkd->bhqk", dout, v64)
+    ds = p * (dp - dpsum)
+    dk = scale * np.einsum("bhqk,bhqd->bhkd", ds, q)
+    dq = scale * np.einsum("bhqk,bhkd->bhqd", ds, k64)
+    group = heads_q // heads_kv
+    if group > 1:
+        b, _, sk, d = dk.shape
+        dk = dk.reshape(b, heads_kv, group, sk, d).sum(axis=2)
+        dv = dv.reshape(b, heads_kv, group, sk, d).sum(axis=2)
+    return dq, dk, dv

@@ -1,0 +1,152 @@
+"""TEST INFRASTRUCTURE ONLY — the parity oracle and the timed CPU baseline.
+
+The oracle is torch's CPU scaled-dot-product attention on float32 upcasts of the SAME
+16-bit-rounded inputs the GPU sees, which is exactly what the reference's GPU tests compare its
+kernels against (tests/test_eager_kernels.py:9495-9535); the logsumexp comes from the CPU flash
+op (``aten::_scaled_dot_product_flash_attention_for_cpu``).  Parity status: see
+``oracle/restatement.py`` — not pinned against the reference's own Mojo kernels (they cannot run
+here), pinned against the reference tests' expectation and an independent float64 restatement.
+
+This module also owns the seeded synthetic inputs for the five benchmark configurations and
+the FLOP convention (forward ``4*B*H*Sq*Sk*D``, halved when causal; backward 2.5x forward —
+benchmarks/test_attention.py:46,163).
+"""
+
+from __future__ import annotations
+
+import dataclasses
+import math
+import os
+import time
+
+import torch
+
+
+@dataclasses.dataclass(frozen=True)
+class Config:
+    name: str
+    dtype: torch.dtype
+    causal: bool
+    B: int
+    Hq: int
+    Hkv: int
+    S: int
+    D: int
+    scale: float
+    backward: bool
+    dist: str  # "normal", "half_normal" (0.5*N(0,1)) or "uniform" (U(-1,1))
+
+    def fwd_flops(self) -> float:
+        f = 4.0 * self.B * self.Hq * self.S * self.S * self.D
+        return f / 2 if self.causal else f
+
+    def bwd_flops(self) -> float:
+        return 2.5 * self.fwd_flops()
+
+    def fwd_bytes(self) -> float:
+        es = torch.empty((), dtype=self.dtype).element_size()
+        qo = 2 * self.B * self.Hq * self.S * self.D * es
+        kv = 2 * self.B * self.Hkv * self.S * self.D * es
+        return qo + kv + self.B * self.Hq * self.S * 4
+
+    def bwd_bytes(self) -> float:
+        es = torch.empty((), dtype=self.dtype).element_size()
+        q_like = 4 * self.B * self.Hq * self.S * self.D * es  # q, out, dout read; dq written
+        kv_like = 4 * self.B * self.Hkv * self.S * self.D * es  # k, v read; dk, dv written
+        return q_like + kv_like + self.B * self.Hq * self.S * 4
+
+
+CONFIGS = {
+    "C1": Config("C1", torch.float32, True, 2, 4, 4, 256, 64, 1 / math.sqrt(64), False, "normal"),
+    "C2": Config("C2", torch.bfloat16, True, 8, 12, 12, 1024, 64, 0.125, True, "normal"),
+    "C3": Config("C3", torch.bfloat16, True, 4, 32, 8, 4096, 128, 1 / math.sqrt(128), True, "half_normal"),
+    "C4": Config("C4", torch.bfloat16, True, 1, 32, 32, 32768, 128, 1 / math.sqrt(128), False, "normal"),
+    "C5": Config("C5", torch.float16, False, 64, 16, 16, 2048, 128, 1 / math.sqrt(128), True, "uniform"),
+}
+
+
+def shard(cfg: Config, rank: int, world: int) -> Config:
+    """The slice of `cfg` that rank `rank` of `world` owns.
+
+    Units are (batch, kv-head group) pairs: the batch is split first, then KV heads (with the
+    query heads that read them); a GQA group is never split.
+    """
+    if world == 1:
+        return cfg
+    if cfg.B % world == 0:
+        return dataclasses.replace(cfg, B=cfg.B // world)
+    if world % cfg.B == 0 and cfg.Hkv % (world // cfg.B) == 0:
+        per = world // cfg.B
+        return dataclasses.replace(cfg, B=1, Hq=cfg.Hq // per, Hkv=cfg.Hkv // per)
+    raise ValueError(f"{cfg.name} does not split over {world} ranks")
+
+
+def make_inputs(cfg: Config, seed: int = 0, B: int | None = None, Hq: int | None = None,
+                Hkv: int | None = None, S: int | None = None):
+    """q, k, v, dout as CPU tensors of cfg.dtype, drawn in that order from one seeded generator
+    (the draw discipline of benchmarks/test_attention.py:36-47,126-128)."""
+    B = cfg.B if B is None else B
+    Hq = cfg.Hq if Hq is None else Hq
+    Hkv = cfg.Hkv if Hkv is None else Hkv
+    S = cfg.S if S is None else S
+    g = torch.Generator().manual_seed(seed)
+
+    def draw(shape):
+        if cfg.dist == "uniform":
+            return torch.rand(shape, generator=g, dtype=torch.float32) * 2 - 1
+        x = torch.randn(shape, generator=g, dtype=torch.float32)
+        return x * 0.5 if cfg.dist == "half_normal" else x
+
+    q = draw((B, Hq, S, cfg.D)).to(cfg.dtype)
+    k = draw((B, Hkv, S, cfg.D)).to(cfg.dtype)
+    v = draw((B, Hkv, S, cfg.D)).to(cfg.dtype)
+    dout = torch.randn((B, Hq, S, cfg.D), generator=g, dtype=torch.float32).to(cfg.dtype)
+    return q, k, v, dout
+
+
+def sdpa_forward(q, k, v, causal: bool, scale: float):
+    """(out fp32, lse fp32) from torch's CPU flash op on fp32 upcasts."""
+    q32, k32, v32 = (t.detach().float().contiguous() for t in (q, k, v))
+    out, lse = torch.ops.aten._scaled_dot_product_flash_attention_for_cpu(
+        q32, k32, v32, 0.0, causal, scale=scale
+    )
+    return out, lse
+
+
+def sdpa_backward(q, k, v, dout, causal: bool, scale: float):
+    """(out, dq, dk, dv) in fp32 via autograd through CPU SDPA on fp32 upcasts."""
+    q32, k32, v32 = (t.detach().float().contiguous().requires_grad_() for t in (q, k, v))
+    out = torch.nn.functional.scaled_dot_product_attention(
+        q32, k32, v32, dropout_p=0.0, is_causal=causal, scale=scale, enable_gqa=q.shape[1] != k.shape[1]
+    )
+    out.backward(dout.detach().float())
+    return out.detach(), q32.grad, k32.grad, v32.grad
+
+
+def time_cpu(cfg: Config, *, backward: bool, sample_heads: int, reps: int = 1, threads: int | None = None):
+    """Time the CPU path on a (B=1, `sample_heads` KV-head groups) slice of `cfg` in its real dtype.
+
+    Returns (TFLOP/s, seconds per rep, threads used, description of the sample).
+    """
+    threads = threads or os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    group = cfg.Hq // cfg.Hkv
+    hkv = max(1, min(sample_heads, cfg.Hkv))
+    q, k, v, dout = make_inputs(cfg, B=1, Hq=hkv * group, Hkv=hkv)
+    flops = 4.0 * 1 * hkv * group * cfg.S * cfg.S * cfg.D * (0.5 if cfg.causal else 1.0)
+    if backward:
+        flops *= 3.5  # forward + backward, the way a training step runs it
+    best = float("inf")
+    for _ in range(max(1, reps)):
+        t0 = time.perf_counter()
+        if backward:
+            qq, kk, vv = (t.clone().requires_grad_() for t in (q, k, v))
+            o = torch.nn.functional.scaled_dot_product_attention(
+                qq, kk, vv, dropout_p=0.0, is_causal=cfg.causal, scale=cfg.scale, enable_gqa=group > 1
+            )
+            o.backward(dout)
+        else:
+            torch.ops.aten._scaled_dot_product_flash_attention_for_cpu(q, k, v, 0.0, cfg.causal, scale=cfg.scale)
+        best = min(best, time.perf_counter() - t0)
+    sample = f"B=1, Hq={hkv * group}, Hkv={hkv}, S={cfg.S}, D={cfg.D}, {'fwd+bwd' if backward else 'fwd'}, best of {reps}"
+    return flops / best / 1e12, best, threads, sample

@@ -1,0 +1,270 @@
+// Host side of the C ABI declared in include/b200fa.h: argument validation (always before
+// any launch, like the reference's bridge does in
+// torch_mojo_backend/eager_flash_attention/fa4_ops.mojo:309-396, 625-663, 857-892),
+// TMA descriptor encoding, kernel selection and launch accounting.
+#include <atomic>
+#include <cmath>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/b200fa.h"
+#include "common.cuh"
+
+namespace b200fa {
+namespace {
+
+std::atomic<uint64_t> g_launches{0};
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode_fn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeFn>(sym);
+    }
+  });
+  return fn;
+}
+
+int elem_size(int dtype) { return dtype == kF32 ? 4 : 2; }
+
+// Checks one (B,H,S,D) view; fills `out`.
+int check_view(const b200fa_tensor4* t, int64_t B, int64_t H, int64_t S, int64_t D, int dtype, View4* out) {
+  if (!t || !t->ptr) return B200FA_ERR_NULL;
+  if (t->shape[0] != B || t->shape[1] != H || t->shape[2] != S || t->shape[3] != D) return B200FA_ERR_BAD_SHAPE;
+  if (t->stride[3] != 1) return B200FA_ERR_BAD_STRIDE;
+  const int es = elem_size(dtype);
+  for (int i = 0; i < 3; ++i) {
+    if (t->stride[i] < 0) return B200FA_ERR_BAD_STRIDE;
+    // rows are moved 16 bytes at a time (TMA boxes, vector stores)
+    if ((t->stride[i] * es) % 16 != 0) return B200FA_ERR_BAD_STRIDE;
+  }
+  if (S > 1 && t->stride[2] < D) return B200FA_ERR_BAD_STRIDE;
+  if (reinterpret_cast<uintptr_t>(t->ptr) % 16 != 0) return B200FA_ERR_MISALIGNED;
+  out->ptr = t->ptr;
+  out->sb = t->stride[0];
+  out->sh = t->stride[1];
+  out->ss = t->stride[2];
+  return B200FA_OK;
+}
+
+struct DeviceGuard {
+  int prev = -1;
+  bool ok = true;
+  explicit DeviceGuard(int device) {
+    if (cudaGetDevice(&prev) != cudaSuccess) { ok = false; return; }
+    if (device != prev && cudaSetDevice(device) != cudaSuccess) ok = false;
+  }
+  ~DeviceGuard() {
+    int cur = -1;
+    if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) cudaSetDevice(prev);
+  }
+};
+
+int check_device_is_sm100(int device) {
+  static int cached[64];
+  static std::once_flag once;
+  std::call_once(once, [] { std::memset(cached, 0, sizeof(cached)); });
+  if (device < 0 || device >= 64) return B200FA_ERR_CUDA;
+  if (cached[device] == 0) {
+    int major = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess)
+      return B200FA_ERR_CUDA;
+    cached[device] = (major == 10) ? 1 : -1;
+  }
+  return cached[device] == 1 ? B200FA_OK : B200FA_ERR_UNSUPPORTED;
+}
+
+size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+
+}  // namespace
+
+bool encode_map_16bit(CUtensorMap* map, const View4& t, int B, int H, int S, int D, int box_rows, bool bf16) {
+  EncodeFn fn = get_encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(S), static_cast<cuuint64_t>(H),
+                        static_cast<cuuint64_t>(B)};
+  // a stride of 0 (size-1 dimension given stride 0) is not encodable: any 16-byte multiple works
+  auto stride_bytes = [&](int64_t s_elems, int64_t fallback) {
+    const int64_t s = (s_elems > 0 ? s_elems : fallback) * 2;
+    return static_cast<cuuint64_t>(s);
+  };
+  const int64_t row = t.ss > 0 ? t.ss : D;
+  cuuint64_t strides[3] = {stride_bytes(t.ss, D), stride_bytes(t.sh, row * S),
+                           stride_bytes(t.sb, row * S * (H > 0 ? H : 1))};
+  cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, t.ptr, dims,
+                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+}  // namespace b200fa
+
+using namespace b200fa;
+
+extern "C" {
+
+int b200fa_version(void) { return B200FA_VERSION; }
+
+uint64_t b200fa_launch_count(void) { return g_launches.load(); }
+
+const char* b200fa_strerror(int code) {
+  switch (code) {
+    case B200FA_OK: return "ok";
+    case B200FA_ERR_BAD_DTYPE: return "unsupported element type (expected fp32, bf16 or fp16)";
+    case B200FA_ERR_BAD_SHAPE: return "tensor shapes are inconsistent or out of range";
+    case B200FA_ERR_BAD_STRIDE: return "tensor strides are unsupported (head_dim stride must be 1, others multiples of 16 bytes)";
+    case B200FA_ERR_MISALIGNED: return "a tensor base address is not 16-byte aligned";
+    case B200FA_ERR_WORKSPACE: return "workspace is missing, misaligned or too small";
+    case B200FA_ERR_UNSUPPORTED: return "configuration is not supported (head_dim must be 64 or 128, Sq == Sk, scale > 0, sm_100 device)";
+    case B200FA_ERR_CUDA: return "a CUDA runtime or driver call failed";
+    case B200FA_ERR_NULL: return "a required pointer is null";
+    case B200FA_ERR_TIMEOUT: return "a kernel gave up waiting on an internal barrier";
+    default: return "unknown b200fa error";
+  }
+}
+
+static int fwd_impl(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_tensor4* v,
+                    const b200fa_tensor4* out, float* lse, int dtype, int causal, float scale, void* stream,
+                    int device, uint32_t* status_word, bool force_simt) {
+  if (!q || !k || !v || !out || !lse) return B200FA_ERR_NULL;
+  if (dtype != kF32 && dtype != kBF16 && dtype != kF16) return B200FA_ERR_BAD_DTYPE;
+  const int64_t B = q->shape[0], Hq = q->shape[1], Sq = q->shape[2], D = q->shape[3];
+  const int64_t Hkv = k->shape[1], Sk = k->shape[2];
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Sq <= 0 || Sk <= 0) return B200FA_ERR_BAD_SHAPE;
+  if (B > 65535 || Hq > 65535 || Sq > (1 << 24)) return B200FA_ERR_BAD_SHAPE;
+  if (D != 64 && D != 128) return B200FA_ERR_UNSUPPORTED;
+  if (Hq % Hkv != 0) return B200FA_ERR_BAD_SHAPE;
+  if (Sq != Sk) return B200FA_ERR_UNSUPPORTED;
+  if (!(scale > 0.f) || !std::isfinite(scale)) return B200FA_ERR_UNSUPPORTED;
+  if (reinterpret_cast<uintptr_t>(lse) % 4 != 0) return B200FA_ERR_MISALIGNED;
+  FwdParams p;
+  std::memset(&p, 0, sizeof(p));
+  int rc;
+  if ((rc = check_view(q, B, Hq, Sq, D, dtype, &p.q)) != B200FA_OK) return rc;
+  if ((rc = check_view(k, B, Hkv, Sk, D, dtype, &p.k)) != B200FA_OK) return rc;
+  if ((rc = check_view(v, B, Hkv, Sk, D, dtype, &p.v)) != B200FA_OK) return rc;
+  if ((rc = check_view(out, B, Hq, Sq, D, dtype, &p.out)) != B200FA_OK) return rc;
+  p.lse = lse;
+  p.B = static_cast<int>(B); p.Hq = static_cast<int>(Hq); p.Hkv = static_cast<int>(Hkv);
+  p.Sq = static_cast<int>(Sq); p.Sk = static_cast<int>(Sk); p.D = static_cast<int>(D);
+  p.causal = causal ? 1 : 0;
+  p.scale = scale;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status_word;
+
+  DeviceGuard guard(device);
+  if (!guard.ok) return B200FA_ERR_CUDA;
+  if ((rc = check_device_is_sm100(device)) != B200FA_OK) return rc;
+  int launches = 0;
+  cudaError_t e = (dtype == kF32 || force_simt)
+                      ? launch_fwd_simt(p, dtype, static_cast<cudaStream_t>(stream), &launches)
+                      : launch_fwd_sm100(p, dtype, static_cast<cudaStream_t>(stream), &launches);
+  g_launches += launches;
+  return e == cudaSuccess ? B200FA_OK : B200FA_ERR_CUDA;
+}
+
+int b200fa_fwd(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_tensor4* v,
+               const b200fa_tensor4* out, float* lse, int dtype, int causal, float scale, void* stream,
+               int device, uint32_t* status_word) {
+  return fwd_impl(q, k, v, out, lse, dtype, causal, scale, stream, device, status_word, false);
+}
+
+int b200fa_fwd_simt(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_tensor4* v,
+                    const b200fa_tensor4* out, float* lse, int dtype, int causal, float scale, void* stream,
+                    int device, uint32_t* status_word) {
+  return fwd_impl(q, k, v, out, lse, dtype, causal, scale, stream, device, status_word, true);
+}
+
+size_t b200fa_bwd_workspace_bytes(int64_t batch, int64_t heads_q, int64_t heads_kv, int64_t seqlen,
+                                  int64_t head_dim, int dtype) {
+  (void)heads_kv;
+  (void)dtype;
+  if (batch <= 0 || heads_q <= 0 || seqlen <= 0 || head_dim <= 0) return 0;
+  const size_t spad = static_cast<size_t>((seqlen + 127) / 128 * 128);
+  const size_t rows = static_cast<size_t>(batch) * heads_q * spad;
+  return 2 * align256(rows * 4) + align256(rows * head_dim * 4);
+}
+
+static int bwd_impl(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_tensor4* v,
+                    const b200fa_tensor4* out, const b200fa_tensor4* dout, const float* lse,
+                    const b200fa_tensor4* dq, const b200fa_tensor4* dk, const b200fa_tensor4* dv, void* workspace,
+                    size_t workspace_bytes, int dtype, int causal, float scale, void* stream, int device,
+                    uint32_t* status_word, bool force_simt) {
+  if (!q || !k || !v || !out || !dout || !lse || !dq || !dk || !dv) return B200FA_ERR_NULL;
+  if (dtype != kF32 && dtype != kBF16 && dtype != kF16) return B200FA_ERR_BAD_DTYPE;
+  const int64_t B = q->shape[0], Hq = q->shape[1], S = q->shape[2], D = q->shape[3];
+  const int64_t Hkv = k->shape[1];
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || S <= 0) return B200FA_ERR_BAD_SHAPE;
+  if (B > 65535 || Hq > 65535 || S > (1 << 24)) return B200FA_ERR_BAD_SHAPE;
+  if (D != 64 && D != 128) return B200FA_ERR_UNSUPPORTED;
+  if (Hq % Hkv != 0) return B200FA_ERR_BAD_SHAPE;
+  if (k->shape[2] != S) return B200FA_ERR_UNSUPPORTED;
+  if (!(scale > 0.f) || !std::isfinite(scale)) return B200FA_ERR_UNSUPPORTED;
+  BwdParams p;
+  std::memset(&p, 0, sizeof(p));
+  int rc;
+  if ((rc = check_view(q, B, Hq, S, D, dtype, &p.q)) != B200FA_OK) return rc;
+  if ((rc = check_view(k, B, Hkv, S, D, dtype, &p.k)) != B200FA_OK) return rc;
+  if ((rc = check_view(v, B, Hkv, S, D, dtype, &p.v)) != B200FA_OK) return rc;
+  if ((rc = check_view(out, B, Hq, S, D, dtype, &p.out)) != B200FA_OK) return rc;
+  if ((rc = check_view(dout, B, Hq, S, D, dtype, &p.dout)) != B200FA_OK) return rc;
+  if ((rc = check_view(dq, B, Hq, S, D, dtype, &p.dq)) != B200FA_OK) return rc;
+  if ((rc = check_view(dk, B, Hkv, S, D, dtype, &p.dk)) != B200FA_OK) return rc;
+  if ((rc = check_view(dv, B, Hkv, S, D, dtype, &p.dv)) != B200FA_OK) return rc;
+  const size_t need = b200fa_bwd_workspace_bytes(B, Hq, Hkv, S, D, dtype);
+  if (!workspace || workspace_bytes < need || reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
+    return B200FA_ERR_WORKSPACE;
+  const size_t spad = static_cast<size_t>((S + 127) / 128 * 128);
+  const size_t rows = static_cast<size_t>(B) * Hq * spad;
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  p.dpsum = reinterpret_cast<float*>(ws);
+  p.lse_log2 = reinterpret_cast<float*>(ws + align256(rows * 4));
+  p.dq_accum = reinterpret_cast<float*>(ws + 2 * align256(rows * 4));
+  p.lse = lse;
+  p.B = static_cast<int>(B); p.Hq = static_cast<int>(Hq); p.Hkv = static_cast<int>(Hkv);
+  p.S = static_cast<int>(S); p.Spad = static_cast<int>(spad); p.D = static_cast<int>(D);
+  p.causal = causal ? 1 : 0;
+  p.scale = scale;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status_word;
+
+  DeviceGuard guard(device);
+  if (!guard.ok) return B200FA_ERR_CUDA;
+  if ((rc = check_device_is_sm100(device)) != B200FA_OK) return rc;
+  int launches = 0;
+  cudaError_t e = (dtype == kF32 || force_simt)
+                      ? launch_bwd_simt(p, dtype, static_cast<cudaStream_t>(stream), &launches)
+                      : launch_bwd_sm100(p, dtype, static_cast<cudaStream_t>(stream), &launches);
+  g_launches += launches;
+  return e == cudaSuccess ? B200FA_OK : B200FA_ERR_CUDA;
+}
+
+int b200fa_bwd(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_tensor4* v,
+               const b200fa_tensor4* out, const b200fa_tensor4* dout, const float* lse,
+               const b200fa_tensor4* dq, const b200fa_tensor4* dk, const b200fa_tensor4* dv, void* workspace,
+               size_t workspace_bytes, int dtype, int causal, float scale, void* stream, int device,
+               uint32_t* status_word) {
+  return bwd_impl(q, k, v, out, dout, lse, dq, dk, dv, workspace, workspace_bytes, dtype, causal, scale, stream,
+                  device, status_word, false);
+}
+
+int b200fa_bwd_simt(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_tensor4* v,
+                    const b200fa_tensor4* out, const b200fa_tensor4* dout, const float* lse,
+                    const b200fa_tensor4* dq, const b200fa_tensor4* dk, const b200fa_tensor4* dv, void* workspace,
+                    size_t workspace_bytes, int dtype, int causal, float scale, void* stream, int device,
+                    uint32_t* status_word) {
+  return bwd_impl(q, k, v, out, dout, lse, dq, dk, dv, workspace, workspace_bytes, dtype, causal, scale, stream,
+                  device, status_word, true);
+}
+
+}  // extern "C"

@@ -108,6 +108,22 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+// 1-D bulk copy global -> shared (both 16-byte aligned, size a multiple of 16 bytes)
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// fire-and-forget fp32 vector add into global memory (address 16-byte aligned)
+__device__ __forceinline__ void red_add_v4(float* gdst, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(reinterpret_cast<uint64_t>(gdst)), "f"(a),
+               "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+
 // ---------------------------------------------------------------------------------------
 // tcgen05: tensor memory management
 // ---------------------------------------------------------------------------------------

@@ -1,0 +1,363 @@
+"""Benchmark of the flash-attention hot path: TFLOP/s of one forward+backward step.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config C3] [--impl ours|reference]
+
+A "step" is one forward and one backward pass of the attention operator over one batch of
+seeded synthetic tensors.  With N > 1 (launched under ``torch.distributed.run``, one rank per
+GPU) every rank owns an independent batch of the same size — the path shards over
+(batch, kv-head group) units with no collective — so scaling is weak and ``value`` is the
+aggregate over all ranks.  FLOPs follow the reference's convention: forward
+``4*B*Hq*S*S*D`` halved when causal, backward 2.5x forward
+(benchmarks/test_attention.py:46,163).
+
+Rank 0 prints ONE JSON line.  ``value`` is timed with CUDA events on tensors already resident
+in HBM; ``e2e`` runs the same step through the public `mojo`-device operator API with pinned
+HOST buffers, host<->device copies inside the timed region; ``roofline`` times the dominant
+kernel (the dK/dV/dQ backward kernel) alone; ``cpu_baseline`` is the CPU oracle timed on the
+host cores on a bounded slice of the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "flash-attn fwd+bwd TFLOP/s (bf16, causal)"
+NOMINAL_BF16_TFLOPS = 2250.0
+FALLBACK_BF16_TFLOPS = 1590.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the backward main kernel on the
+# bench workload, from the ncu capture summarised in profiles/ (None until captured).
+BWD_MAIN_DRAM_TRAFFIC_BYTES = None
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
+    except Exception:
+        return FALLBACK_BF16_TFLOPS, 1400.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.samples: list[list[str]] = []
+        self._stop = threading.Event()
+        self._thread = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(
+                    ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits"],
+                    capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.samples.append([x.strip() for x in out.splitlines()[0].split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.1)
+
+    def __enter__(self):
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=10)
+
+    def summary(self):
+        clocks, max_clocks, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                clocks.append(float(s[0]))
+                max_clocks.append(float(s[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, val in zip(names, s[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {
+            "sm_mhz": statistics.median(clocks) if clocks else None,
+            "sm_max_mhz": max(max_clocks) if max_clocks else None,
+            "reasons": sorted(reasons),
+            "samples": len(clocks),
+        }
+
+
+def dist_setup(n_gpus: int):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def barrier(world: int):
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(x: float, world: int) -> float:
+    if world == 1:
+        return x
+    import torch.distributed as dist
+
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def run_ours(args):
+    from oracle import sdpa_oracle as O  # input generation + (rank 0, N=1) the cpu_baseline leg
+    from torch_mojo_backend_b200 import _lib, raw
+
+    rank, world, local = dist_setup(args.gpus)
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    cfg = O.CONFIGS[args.config]
+    do_bwd = cfg.backward
+    q, k, v, dout = (t.to(dev) for t in O.make_inputs(cfg, seed=rank))
+    out = torch.empty_like(q)
+    lse = torch.empty((cfg.B, cfg.Hq, cfg.S), dtype=torch.float32, device=dev)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    code = raw.dtype_code(cfg.dtype)
+    ws = torch.empty((_lib.bwd_workspace_bytes(cfg.B, cfg.Hq, cfg.Hkv, cfg.S, cfg.D, code),), dtype=torch.uint8,
+                     device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def step():
+        raw.flash_fwd(q, k, v, causal=cfg.causal, scale=cfg.scale, out=out, lse=lse, status=status)
+        if do_bwd:
+            raw.flash_bwd(dout, q, k, v, out, lse, causal=cfg.causal, scale=cfg.scale, dq=dq, dk=dk, dv=dv,
+                          workspace=ws, status=status)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier(world)
+    launches0 = _lib.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ef0, ef1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as sampler:
+        barrier(world)
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        barrier(world)
+        total_ms = max_over_ranks(e0.elapsed_time(e1), world)
+        # forward-only and main-backward-kernel-only timings explain the step number
+        ef0.record()
+        for _ in range(args.steps):
+            raw.flash_fwd(q, k, v, causal=cfg.causal, scale=cfg.scale, out=out, lse=lse, status=status)
+        ef1.record()
+        torch.cuda.synchronize()
+        fwd_ms = ef0.elapsed_time(ef1) / args.steps
+        bwd_main_ms = None
+        if do_bwd:
+            eb0, eb1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            eb0.record()
+            for _ in range(args.steps):
+                raw.flash_bwd(dout, q, k, v, out, lse, causal=cfg.causal, scale=cfg.scale, dq=dq, dk=dk, dv=dv,
+                              workspace=ws, status=status, parts=2)
+            eb1.record()
+            torch.cuda.synchronize()
+            bwd_main_ms = eb0.elapsed_time(eb1) / args.steps
+    launches = (_lib.launch_count() - launches0)
+    timed_launches = args.steps * (1 + (3 if do_bwd else 0))
+    if int(status.item()) != 0:
+        raise RuntimeError(f"kernel status word is 0x{int(status.item()) & 0xffffffff:x}")
+
+    ms_per_step = total_ms / args.steps
+    step_flops = cfg.fwd_flops() + (cfg.bwd_flops() if do_bwd else 0.0)
+    value = world * step_flops / (ms_per_step * 1e-3) / 1e12
+
+    # ---- end to end through the public operator API on the mojo device, host buffers in/out
+    e2e = run_e2e(cfg, rank, world, local, args)
+
+    burst, sustained, peak_src = load_peaks()
+    if do_bwd:
+        dom_flops, dom_ms, dom_name = cfg.bwd_flops(), bwd_main_ms, "bwd_kernel (dK/dV/dQ tcgen05 pipeline)"
+    else:
+        dom_flops, dom_ms, dom_name = cfg.fwd_flops(), fwd_ms, "fwd_kernel"
+    achieved = dom_flops / (dom_ms * 1e-3) / 1e12
+    roofline = {
+        "bound": "tensor", "kernel": dom_name, "achieved": round(achieved, 2), "peak": burst, "unit": "TFLOP/s",
+        "frac": round(achieved / burst, 4), "peak_source": f"of {peak_src} (cuBLAS bf16 burst)",
+        "frac_of_nominal_2250": round(achieved / NOMINAL_BF16_TFLOPS, 4),
+        "traffic": BWD_MAIN_DRAM_TRAFFIC_BYTES if do_bwd else None,
+        "ms_per_launch": round(dom_ms, 4),
+    }
+    detail = {
+        "fwd_ms": round(fwd_ms, 4), "fwd_tflops": round(cfg.fwd_flops() / (fwd_ms * 1e-3) / 1e12, 2),
+        "fwd_frac_of_nominal_2250": round(cfg.fwd_flops() / (fwd_ms * 1e-3) / 1e12 / NOMINAL_BF16_TFLOPS, 4),
+    }
+    if do_bwd:
+        bwd_ms = ms_per_step - fwd_ms
+        detail.update({
+            "bwd_ms": round(bwd_ms, 4), "bwd_tflops": round(cfg.bwd_flops() / (bwd_ms * 1e-3) / 1e12, 2),
+            "bwd_frac_of_nominal_2250": round(cfg.bwd_flops() / (bwd_ms * 1e-3) / 1e12 / NOMINAL_BF16_TFLOPS, 4),
+            "bwd_main_kernel_ms": round(bwd_main_ms, 4),
+        })
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        tf, secs, threads, sample = O.time_cpu(cfg, backward=do_bwd, sample_heads=args.cpu_sample_heads, reps=2)
+        cpu_baseline = {"value": round(tf, 4), "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                        "sample": sample + f" ({secs:.2f} s)"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": str(cfg.dtype).replace("torch.", ""),
+            "data": "synthetic",
+            "config": {
+                "workload": f"{cfg.name}: {'causal' if cfg.causal else 'non-causal'} "
+                            f"{'fwd+bwd' if do_bwd else 'fwd'} B={cfg.B} Hq={cfg.Hq} Hkv={cfg.Hkv} S={cfg.S} "
+                            f"D={cfg.D} per GPU",
+                "l2": "inputs larger than L2 (no flush needed)" if cfg.fwd_bytes() > 126e6
+                      else "working set fits in L2 (L2-hot number)",
+                "seed": "torch.Generator().manual_seed(rank); q,k,v,dO drawn in that order",
+            },
+            "frac_of_nominal_2250": round(value / world / NOMINAL_BF16_TFLOPS, 4),
+            "detail": detail, "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
+            "gpu_launches": int(launches), "gpu_launches_in_step_region": int(timed_launches),
+            "clocks": sampler.summary(),
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+
+
+def run_e2e(cfg, rank, world, local, args):
+    """Same step through F.scaled_dot_product_attention on the `mojo` device: pinned host
+    tensors in, out and gradients read back to the host, all inside the timed region."""
+    import torch_mojo_backend_b200 as tmb
+    from oracle import sdpa_oracle as O
+
+    tmb.register_mojo_devices()
+    torch.mojo.set_device(local)
+    host = [t.pin_memory() for t in O.make_inputs(cfg, seed=rank)]
+    hq, hk, hv, hdo = host
+    steps = max(1, min(args.steps, 5))
+    gqa = cfg.Hq != cfg.Hkv
+    h2d = sum(t.numel() * t.element_size() for t in ((hq, hk, hv, hdo) if cfg.backward else (hq, hk, hv)))
+    d2h = hq.numel() * hq.element_size()
+    if cfg.backward:
+        d2h += sum(t.numel() * t.element_size() for t in (hq, hk, hv))
+
+    def step():
+        dev = torch.device("mojo", local)
+        q = hq.to(dev, non_blocking=True)
+        k = hk.to(dev, non_blocking=True)
+        v = hv.to(dev, non_blocking=True)
+        if cfg.backward:
+            for t in (q, k, v):
+                t.requires_grad_()
+            do = hdo.to(dev, non_blocking=True)
+        out = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=cfg.causal, scale=cfg.scale,
+                                                               enable_gqa=gqa)
+        results = [out.detach().to("cpu", non_blocking=True)]
+        if cfg.backward:
+            out.backward(do)
+            results += [t.grad.to("cpu", non_blocking=True) for t in (q, k, v)]
+        return results
+
+    for _ in range(2):
+        step()
+    barrier(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        res = step()
+    e1.record()
+    barrier(world)
+    ms = max_over_ranks(e0.elapsed_time(e1), world) / steps
+    flops = cfg.fwd_flops() + (cfg.bwd_flops() if cfg.backward else 0.0)
+    del res
+    return {"value": round(world * flops / (ms * 1e-3) / 1e12, 2), "unit": "TFLOP/s", "ms_per_step": round(ms, 3),
+            "steps": steps, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+            "api": "F.scaled_dot_product_attention + backward on mojo tensors; pinned host in, host out"}
+
+
+def run_reference(args):
+    """The reference arm: the reference's own path cannot be built here (it needs the Mojo
+    toolchain), so — as its tests do — torch's CPU SDPA stands in, timed on all host cores on a
+    bounded slice of the same workload.  Only rank 0 works."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import sdpa_oracle as O
+
+    cfg = O.CONFIGS[args.config]
+    threads = os.cpu_count() or 1
+    vals, secs_all, sample = [], [], ""
+    for i in range(args.warmup + args.steps):
+        tf, secs, threads, sample = O.time_cpu(cfg, backward=cfg.backward, sample_heads=args.cpu_sample_heads, reps=1,
+                                               threads=threads)
+        if i >= args.warmup:
+            vals.append(tf)
+            secs_all.append(secs)
+    value = statistics.median(vals)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(value, 4), "unit": "TFLOP/s",
+        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(1e3 * statistics.median(secs_all), 2), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": str(cfg.dtype).replace("torch.", ""), "data": "synthetic",
+        "config": {"workload": f"{cfg.name} (CPU slice: {sample})"},
+        "cpu_baseline": {"value": round(value, 4), "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": round(value, 4), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "reference's Mojo FA4 build is not installable offline and rejects sm_100; torch CPU SDPA "
+                "(the oracle the reference's own tests use) is timed instead",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--config", default="C3", choices=["C1", "C2", "C3", "C4", "C5"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-sample-heads", type=int, default=2)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -111,6 +111,18 @@ int b200fa_bwd_simt(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200
                     void* workspace, size_t workspace_bytes, int dtype, int causal, float scale,
                     void* stream, int device, uint32_t* status_word);
 
+/*
+ * b200fa_bwd restricted to a subset of its three kernels, for timing one kernel alone with
+ * CUDA events: `parts` is a bit mask, 1 = preprocess, 2 = the dK/dV/dQ tensor-core kernel,
+ * 4 = dQ conversion (7 == b200fa_bwd).  16-bit dtypes only.  Results are only meaningful when
+ * the parts are run in order; it has no counterpart in the reference.
+ */
+int b200fa_bwd_parts(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_tensor4* v,
+                     const b200fa_tensor4* out, const b200fa_tensor4* dout, const float* lse,
+                     const b200fa_tensor4* dq, const b200fa_tensor4* dk, const b200fa_tensor4* dv,
+                     void* workspace, size_t workspace_bytes, int dtype, int causal, float scale,
+                     void* stream, int device, uint32_t* status_word, int parts);
+
 /* Human-readable text for a B200FA_ERR_* code (static storage). */
 const char* b200fa_strerror(int code);
 

@@ -1,0 +1,120 @@
+"""The C-ABI library loads, exports every declared symbol and validates before launching.
+
+No compute call happens here: every b200fa_fwd / b200fa_bwd invocation below is rejected by
+argument validation, which the library performs before it touches CUDA."""
+
+import ctypes
+import os
+import re
+
+import pytest
+
+from torch_mojo_backend_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "b200fa.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(b200fa_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_and_binding_agree():
+    assert declared_symbols() == sorted(_lib.EXPORTED_SYMBOLS)
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _lib.load()
+    for name in declared_symbols():
+        assert hasattr(lib, name), name
+    assert _lib.version() == 1
+    assert _lib.launch_count() == 0 or _lib.launch_count() > 0
+
+
+def test_strerror_covers_all_codes():
+    seen = set()
+    for code in range(0, -10, -1):
+        msg = _lib.strerror(code)
+        assert msg and "unknown" not in msg
+        seen.add(msg)
+    assert len(seen) == 10
+    assert "unknown" in _lib.strerror(-99)
+
+
+def test_workspace_formula():
+    # 2 x (B*Hq*Spad) fp32 statistics + (B*Hq*Spad*D) fp32 dQ accumulator, Spad = ceil(S/128)*128
+    # (the reference's scratch: aten_fast.py:7314-7324)
+    B, Hq, Hkv, S, D = 8, 12, 12, 1024, 64
+    rows = B * Hq * 1024
+    assert _lib.bwd_workspace_bytes(B, Hq, Hkv, S, D, _lib.BF16) == 2 * rows * 4 + rows * D * 4
+    assert _lib.bwd_workspace_bytes(1, 1, 1, 65, 64, _lib.BF16) == 2 * 512 + 128 * 64 * 4
+    assert _lib.bwd_workspace_bytes(0, 1, 1, 65, 64, _lib.BF16) == 0
+
+
+def _t4(ptr, shape, stride=None):
+    if stride is None:
+        stride = (shape[1] * shape[2] * shape[3], shape[2] * shape[3], shape[3], 1)
+    return _lib.Tensor4.make(ptr, shape, stride)
+
+
+FAKE = 0x7F0000000000  # never dereferenced: validation rejects the call first
+
+
+@pytest.mark.parametrize(
+    "mutate,expected",
+    [
+        (dict(dtype=7), _lib.ERR_BAD_DTYPE),
+        (dict(q_shape=(1, 2, 128, 96)), _lib.ERR_UNSUPPORTED),  # head_dim not 64/128
+        (dict(k_shape=(1, 3, 128, 64), q_shape=(1, 4, 128, 64)), _lib.ERR_BAD_SHAPE),  # Hq % Hkv
+        (dict(k_shape=(1, 2, 256, 64)), _lib.ERR_UNSUPPORTED),  # Sq != Sk
+        (dict(scale=0.0), _lib.ERR_UNSUPPORTED),
+        (dict(scale=float("nan")), _lib.ERR_UNSUPPORTED),
+        (dict(q_stride=(16384, 8192, 64, 2)), _lib.ERR_BAD_STRIDE),  # head_dim stride must be 1
+        (dict(q_stride=(16388, 8196, 68, 1)), _lib.ERR_BAD_STRIDE),  # rows not 16-byte multiples
+        (dict(q_ptr=FAKE + 2), _lib.ERR_MISALIGNED),
+        (dict(q_ptr=0), _lib.ERR_NULL),
+        (dict(lse=0), _lib.ERR_NULL),
+        (dict(v_shape=(1, 2, 128, 128)), _lib.ERR_BAD_SHAPE),
+    ],
+)
+def test_forward_validates_before_launch(mutate, expected):
+    q_shape = mutate.get("q_shape", (1, 2, 128, 64))
+    k_shape = mutate.get("k_shape", (1, 2, 128, 64))
+    v_shape = mutate.get("v_shape", k_shape)
+    q = _t4(mutate.get("q_ptr", FAKE), q_shape, mutate.get("q_stride"))
+    k = _t4(FAKE + 0x100000, k_shape)
+    v = _t4(FAKE + 0x200000, v_shape)
+    out = _t4(FAKE + 0x300000, q_shape)
+    before = _lib.launch_count()
+    rc = _lib.fwd(q, k, v, out, mutate.get("lse", FAKE + 0x400000), mutate.get("dtype", _lib.BF16), True,
+                  mutate.get("scale", 0.125), 0, 0)
+    assert rc == expected, _lib.strerror(rc)
+    assert _lib.launch_count() == before
+
+
+def test_backward_rejects_small_or_missing_workspace():
+    shape = (1, 2, 128, 64)
+    t = [_t4(FAKE + i * 0x100000, shape) for i in range(8)]
+    need = _lib.bwd_workspace_bytes(1, 2, 2, 128, 64, _lib.BF16)
+    for ws_ptr, ws_bytes in ((0, need), (FAKE + 0x900000, need - 1), (FAKE + 0x900010, need)):
+        rc = _lib.bwd(t[0], t[1], t[2], t[3], t[4], FAKE + 0xA00000, t[5], t[6], t[7], ws_ptr, ws_bytes, _lib.BF16,
+                      True, 0.125, 0, 0)
+        assert rc == _lib.ERR_WORKSPACE
+
+
+def test_valid_call_without_gpu_reports_cuda_error_not_success():
+    """With valid arguments and no device the library must fail loudly (never pretend)."""
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present; this checks the no-GPU failure mode")
+    shape = (1, 2, 128, 64)
+    t = [_t4(FAKE + i * 0x100000, shape) for i in range(4)]
+    rc = _lib.fwd(t[0], t[1], t[2], t[3], FAKE + 0x800000, _lib.BF16, True, 0.125, 0, 0)
+    assert rc in (_lib.ERR_CUDA, _lib.ERR_UNSUPPORTED)
+
+
+def test_struct_layout_matches_header():
+    assert ctypes.sizeof(_lib.Tensor4) == 8 + 32 + 32
+    assert _lib.Tensor4.shape.offset == 8 and _lib.Tensor4.stride.offset == 40

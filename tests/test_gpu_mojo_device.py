@@ -1,0 +1,85 @@
+"""The operator API on the `mojo` device, end to end on a GPU (``-m gpu``): the reference's
+public contract from tests/test_eager_kernels.py:9437-9585 and :10044-10071."""
+
+import pytest
+import torch
+
+from oracle import sdpa_oracle as O
+from tests.helpers import TOL_16BIT, TOL_LSE, assert_within, load_golden
+from torch_mojo_backend_b200 import flash_ops
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def mojo(mojo_registered):
+    return torch.device("mojo", 0)
+
+
+@pytest.mark.parametrize("name", ["fused_bf16_d64", "fused_f16_d128", "fused_bf16_d128_b2"])
+def test_nanogpt_layout_forward_backward(mojo, name):
+    """Fused-QKV gapped views, SDPA with grad, sequence-major output, native flash backward."""
+    meta, _, _, _, dout, exp = load_golden(name)
+    b, h, s, d = meta["B"], meta["Hq"], meta["S"], meta["D"]
+    fused = meta["fused"].to(mojo)
+    q, k, v = (p.view(b, s, h, d).transpose(1, 2) for p in fused.split(h * d, dim=2))
+    for t in (q, k, v):
+        t.requires_grad_()
+        assert not t._is_contiguous
+    before = dict(flash_ops.CALL_COUNTERS)
+    out = torch.nn.functional.scaled_dot_product_attention(q, k, v, dropout_p=0.0, is_causal=True)
+    assert type(out.grad_fn).__name__ == "ScaledDotProductFlashAttentionBackward0"
+    assert out.dtype == meta["dtype"]
+    assert not out._is_contiguous and out.transpose(1, 2)._is_contiguous
+    out.backward(dout.to(mojo))
+    after = flash_ops.CALL_COUNTERS
+    assert after["aten::_scaled_dot_product_flash_attention"] == before["aten::_scaled_dot_product_flash_attention"] + 1
+    assert (after["aten::_scaled_dot_product_flash_attention_backward"]
+            == before["aten::_scaled_dot_product_flash_attention_backward"] + 1)
+    assert_within("out", out.cpu(), exp["out"], TOL_16BIT, meta["dtype"])
+    for t, key in ((q, "dq"), (k, "dk"), (v, "dv")):
+        assert t.grad is not None
+        assert_within(key, t.grad.cpu(), exp[key], TOL_16BIT, meta["dtype"])
+    # the caller's re-assembly is a free view of the sequence-major output
+    y = out.transpose(1, 2).contiguous().view(b, s, h * d)
+    assert y._ptr == out._ptr
+
+
+def test_direct_flash_op_returns_a_real_logsumexp(mojo):
+    meta, q, k, v, _, exp = load_golden("gqa_bf16_s256")
+    res = torch.ops.aten._scaled_dot_product_flash_attention.default(
+        q.to(mojo), k.to(mojo), v.to(mojo), 0.0, True, False, scale=meta["scale"])
+    assert len(res) == 9 and res[2] is None and res[3] is None and res[4] == meta["S"]
+    assert_within("out", res[0].cpu(), exp["out"], TOL_16BIT, meta["dtype"])
+    assert_within("lse", res[1].cpu(), exp["lse"], TOL_LSE)
+
+
+def test_autocast_block_runs_the_bf16_kernel(mojo):
+    g = torch.Generator().manual_seed(11)
+    q, k, v = (torch.randn(2, 4, 256, 64, generator=g) * 0.5 for _ in range(3))
+    ref, _ = O.sdpa_forward(q.bfloat16(), k.bfloat16(), v.bfloat16(), True, 0.125)
+    with torch.autocast("mojo", dtype=torch.bfloat16):
+        out = torch.nn.functional.scaled_dot_product_attention(q.to(mojo), k.to(mojo), v.to(mojo), is_causal=True)
+    assert out.dtype == torch.bfloat16
+    assert_within("out", out.cpu(), ref, TOL_16BIT, torch.bfloat16)
+
+
+def test_in_place_mutation_of_saved_tensors_raises(mojo):
+    """Generated autograd owns the saves, so its version-counter check fires
+    (reference: tests/test_eager_kernels.py:10044-10071)."""
+    q = (torch.randn(1, 2, 128, 64) * 0.5).bfloat16().to(mojo).requires_grad_()
+    k = (torch.randn(1, 2, 128, 64) * 0.5).bfloat16().to(mojo)
+    v = (torch.randn(1, 2, 128, 64) * 0.5).bfloat16().to(mojo)
+    out = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True)
+    k.add_(k)
+    with pytest.raises(RuntimeError, match="modified by an inplace operation"):
+        out.backward(torch.ones(1, 2, 128, 64).bfloat16().to(mojo))
+
+
+def test_zero_copy_interop_with_cuda_tensors(mojo_registered):
+    x = torch.arange(24, dtype=torch.float32, device="cuda").view(2, 3, 4)
+    m = mojo_registered.from_cuda(x)
+    assert m._ptr == x.data_ptr() and torch.equal(m.cpu(), x.cpu())
+    back = torch.from_dlpack(m)
+    assert back.data_ptr() == x.data_ptr()
+    assert mojo_registered.to_cuda(m.transpose(0, 1)).data_ptr() == x.data_ptr()

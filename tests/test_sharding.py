@@ -1,0 +1,66 @@
+"""Multi-GPU host logic on CPU: how configs shard over ranks, and the world-size-2 gather that
+validates shards against the unsharded oracle (gloo; the GPU run uses NCCL for the same step)."""
+
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import sdpa_oracle as O
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_shard_never_splits_a_gqa_group():
+    c3 = O.CONFIGS["C3"]
+    for world in (1, 2, 4, 8):
+        s = O.shard(c3, 0, world)
+        assert s.Hq // s.Hkv == c3.Hq // c3.Hkv
+        assert s.B * s.Hkv * world == c3.B * c3.Hkv
+    c4 = O.shard(O.CONFIGS["C4"], 3, 8)
+    assert (c4.B, c4.Hq, c4.Hkv) == (1, 4, 4)
+    c5 = O.shard(O.CONFIGS["C5"], 0, 8)
+    assert (c5.B, c5.Hq) == (8, 16)
+    c2 = O.shard(O.CONFIGS["C2"], 0, 8)
+    assert c2.B == 1 and c2.Hq == 12
+    with pytest.raises(ValueError):
+        O.shard(O.CONFIGS["C3"], 0, 3)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, result_path):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    # every rank derives the full problem from the seed and takes its (batch) slice: shards are
+    # bit-identical to the corresponding rows of the single-process run
+    B, H, S, D = 4, 2, 64, 64
+    g = torch.Generator().manual_seed(0)
+    q, k, v = (torch.randn(B, H, S, D, generator=g) for _ in range(3))
+    per = B // world
+    sl = slice(rank * per, (rank + 1) * per)
+    out, lse = O.sdpa_forward(q[sl], k[sl], v[sl], True, 0.125)
+    gathered = [torch.empty_like(out) for _ in range(world)]
+    dist.all_gather(gathered, out)
+    t = torch.tensor([float(rank + 1)])
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        full, _ = O.sdpa_forward(q, k, v, True, 0.125)
+        torch.save({"err": (torch.cat(gathered) - full).abs().max().item(), "max": t.item()}, result_path)
+    dist.destroy_process_group()
+
+
+def test_world_size_two_gather_matches_unsharded(tmp_path):
+    path = str(tmp_path / "result.pt")
+    mp.spawn(_worker, args=(2, _free_port(), path), nprocs=2, join=True)
+    res = torch.load(path)
+    assert res["err"] < 1e-6 and res["max"] == 2.0

@@ -36,6 +36,7 @@ EXPORTED_SYMBOLS = (
     "b200fa_bwd",
     "b200fa_fwd_simt",
     "b200fa_bwd_simt",
+    "b200fa_bwd_parts",
     "b200fa_strerror",
     "b200fa_version",
     "b200fa_launch_count",
@@ -91,6 +92,8 @@ def load() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = bwd_args
         fn.restype = ctypes.c_int
+    lib.b200fa_bwd_parts.argtypes = bwd_args + [ctypes.c_int]
+    lib.b200fa_bwd_parts.restype = ctypes.c_int
     lib.b200fa_bwd_workspace_bytes.argtypes = [ctypes.c_int64] * 5 + [ctypes.c_int]
     lib.b200fa_bwd_workspace_bytes.restype = ctypes.c_size_t
     lib.b200fa_strerror.argtypes = [ctypes.c_int]
@@ -130,8 +133,16 @@ def fwd(q: Tensor4, k: Tensor4, v: Tensor4, out: Tensor4, lse_ptr: int, dtype: i
 
 def bwd(q: Tensor4, k: Tensor4, v: Tensor4, out: Tensor4, dout: Tensor4, lse_ptr: int, dq: Tensor4,
         dk: Tensor4, dv: Tensor4, workspace_ptr: int, workspace_bytes: int, dtype: int, causal: bool,
-        scale: float, stream: int, device: int, status_ptr: int = 0, *, simt: bool = False) -> int:
-    """Raw backward call; returns the library's status code."""
+        scale: float, stream: int, device: int, status_ptr: int = 0, *, simt: bool = False,
+        parts: int = 7) -> int:
+    """Raw backward call; returns the library's status code.  `parts` != 7 runs a subset of
+    the three backward kernels (see b200fa_bwd_parts)."""
+    if parts != 7:
+        return load().b200fa_bwd_parts(
+            ctypes.byref(q), ctypes.byref(k), ctypes.byref(v), ctypes.byref(out), ctypes.byref(dout),
+            ctypes.c_void_p(lse_ptr), ctypes.byref(dq), ctypes.byref(dk), ctypes.byref(dv),
+            ctypes.c_void_p(workspace_ptr), ctypes.c_size_t(workspace_bytes), dtype, 1 if causal else 0,
+            ctypes.c_float(scale), ctypes.c_void_p(stream), device, ctypes.c_void_p(status_ptr), parts)
     fn = load().b200fa_bwd_simt if simt else load().b200fa_bwd
     return fn(ctypes.byref(q), ctypes.byref(k), ctypes.byref(v), ctypes.byref(out), ctypes.byref(dout),
               ctypes.c_void_p(lse_ptr), ctypes.byref(dq), ctypes.byref(dk), ctypes.byref(dv),

@@ -199,7 +199,7 @@ static int bwd_impl(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200
                     const b200fa_tensor4* out, const b200fa_tensor4* dout, const float* lse,
                     const b200fa_tensor4* dq, const b200fa_tensor4* dk, const b200fa_tensor4* dv, void* workspace,
                     size_t workspace_bytes, int dtype, int causal, float scale, void* stream, int device,
-                    uint32_t* status_word, bool force_simt) {
+                    uint32_t* status_word, bool force_simt, int parts = 7) {
   if (!q || !k || !v || !out || !dout || !lse || !dq || !dk || !dv) return B200FA_ERR_NULL;
   if (dtype != kF32 && dtype != kBF16 && dtype != kF16) return B200FA_ERR_BAD_DTYPE;
   const int64_t B = q->shape[0], Hq = q->shape[1], S = q->shape[2], D = q->shape[3];
@@ -237,6 +237,7 @@ static int bwd_impl(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200
   p.scale = scale;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status_word;
+  p.parts = parts;
 
   DeviceGuard guard(device);
   if (!guard.ok) return B200FA_ERR_CUDA;
@@ -256,6 +257,16 @@ int b200fa_bwd(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_te
                uint32_t* status_word) {
   return bwd_impl(q, k, v, out, dout, lse, dq, dk, dv, workspace, workspace_bytes, dtype, causal, scale, stream,
                   device, status_word, false);
+}
+
+int b200fa_bwd_parts(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_tensor4* v,
+                     const b200fa_tensor4* out, const b200fa_tensor4* dout, const float* lse,
+                     const b200fa_tensor4* dq, const b200fa_tensor4* dk, const b200fa_tensor4* dv, void* workspace,
+                     size_t workspace_bytes, int dtype, int causal, float scale, void* stream, int device,
+                     uint32_t* status_word, int parts) {
+  if (dtype == kF32 || parts < 1 || parts > 7) return B200FA_ERR_UNSUPPORTED;
+  return bwd_impl(q, k, v, out, dout, lse, dq, dk, dv, workspace, workspace_bytes, dtype, causal, scale, stream,
+                  device, status_word, false, parts);
 }
 
 int b200fa_bwd_simt(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_tensor4* v,

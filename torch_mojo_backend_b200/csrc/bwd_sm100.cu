@@ -490,9 +490,12 @@ cudaError_t launch_one(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
   constexpr int kRowsPerWarp = 32 / (kD / 8);
   const int64_t total_rows = static_cast<int64_t>(p.B) * p.Hq * p.Spad;
   const int64_t pre_warps = (total_rows + kRowsPerWarp - 1) / kRowsPerWarp;
-  bwd_preprocess_kernel<kD, kBf16><<<static_cast<unsigned>((pre_warps + 7) / 8), 256, 0, stream>>>(p);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return e;
+  cudaError_t e = cudaSuccess;
+  if (p.parts & 1) {
+    bwd_preprocess_kernel<kD, kBf16><<<static_cast<unsigned>((pre_warps + 7) / 8), 256, 0, stream>>>(p);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+  }
 
   auto kern = bwd_kernel<kD, kBf16, kCausal>;
   static bool attr_set[16] = {};
@@ -503,14 +506,18 @@ cudaError_t launch_one(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  dim3 grid((p.S + kTile - 1) / kTile, p.Hkv, p.B);
-  kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(mq, mk, mv, mdo, p);
-  e = cudaGetLastError();
-  if (e != cudaSuccess) return e;
-
-  const int64_t total_vec = static_cast<int64_t>(p.B) * p.Hq * p.S * (kD / 8);
-  bwd_convert_kernel<kD, kBf16><<<static_cast<unsigned>((total_vec + 255) / 256), 256, 0, stream>>>(p);
-  return cudaGetLastError();
+  if (p.parts & 2) {
+    dim3 grid((p.S + kTile - 1) / kTile, p.Hkv, p.B);
+    kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(mq, mk, mv, mdo, p);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+  }
+  if (p.parts & 4) {
+    const int64_t total_vec = static_cast<int64_t>(p.B) * p.Hq * p.S * (kD / 8);
+    bwd_convert_kernel<kD, kBf16><<<static_cast<unsigned>((total_vec + 255) / 256), 256, 0, stream>>>(p);
+    e = cudaGetLastError();
+  }
+  return e;
 }
 
 }  // namespace
@@ -532,7 +539,7 @@ cudaError_t launch_bwd_sm100(const BwdParams& p, int dtype, cudaStream_t stream,
     else      { if (p.causal) B200FA_DISPATCH(64, false, true); else B200FA_DISPATCH(64, false, false); }
   }
 #undef B200FA_DISPATCH
-  if (e == cudaSuccess && launches) *launches += 3;
+  if (e == cudaSuccess && launches) *launches += (p.parts & 1) + ((p.parts >> 1) & 1) + ((p.parts >> 2) & 1);
   return e;
 }
 

@@ -34,6 +34,7 @@ struct BwdParams {
   float scale;
   float scale_log2;
   uint32_t* status;
+  int parts;  // bit 0 preprocess, bit 1 main kernel, bit 2 dQ convert (7 = the whole backward)
 };
 
 // dtype tags shared with the C header

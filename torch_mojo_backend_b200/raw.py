@@ -63,7 +63,7 @@ def flash_fwd(q, k, v, *, causal: bool, scale: float | None = None, out=None, ls
 
 
 def flash_bwd(dout, q, k, v, out, lse, *, causal: bool, scale: float | None = None, dq=None, dk=None,
-              dv=None, workspace=None, status=None, simt: bool = False):
+              dv=None, workspace=None, status=None, simt: bool = False, parts: int = 7):
     """dq, dk, dv = attention backward on CUDA tensors shaped (B, H, S, D)."""
     if q.device.type != "cuda":
         raise RuntimeError("b200fa kernels need CUDA memory; there is no CPU implementation")
@@ -84,7 +84,7 @@ def flash_bwd(dout, q, k, v, out, lse, *, causal: bool, scale: float | None = No
     stream, dev = _stream_and_device(q)
     rc = _lib.bwd(t4(q), t4(k), t4(v), t4(out), t4(dout), lse.data_ptr(), t4(dq), t4(dk), t4(dv),
                   workspace.data_ptr(), workspace.numel() * workspace.element_size(), code, causal, float(scale),
-                  stream, dev, status.data_ptr() if status is not None else 0, simt=simt)
+                  stream, dev, status.data_ptr() if status is not None else 0, simt=simt, parts=parts)
     if rc != _lib.OK:
         raise _lib.B200FAError(rc, "b200fa_bwd")
     return dq, dk, dv

@@ -126,6 +126,10 @@ int b200fa_bwd_parts(const b200fa_tensor4* q, const b200fa_tensor4* k, const b20
 /* Human-readable text for a B200FA_ERR_* code (static storage). */
 const char* b200fa_strerror(int code);
 
+/* Name and text of the CUDA error behind the calling thread's most recent B200FA_ERR_CUDA
+ * (thread-local static storage; empty if none). */
+const char* b200fa_last_error_detail(void);
+
 /* B200FA_VERSION the library was built from. */
 int b200fa_version(void);
 

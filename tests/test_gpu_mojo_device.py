@@ -25,12 +25,12 @@ def test_nanogpt_layout_forward_backward(mojo, name):
     q, k, v = (p.view(b, s, h, d).transpose(1, 2) for p in fused.split(h * d, dim=2))
     for t in (q, k, v):
         t.requires_grad_()
-        assert not t._is_contiguous
+        assert h == 1 or not t._is_contiguous
     before = dict(flash_ops.CALL_COUNTERS)
     out = torch.nn.functional.scaled_dot_product_attention(q, k, v, dropout_p=0.0, is_causal=True)
     assert type(out.grad_fn).__name__ == "ScaledDotProductFlashAttentionBackward0"
     assert out.dtype == meta["dtype"]
-    assert not out._is_contiguous and out.transpose(1, 2)._is_contiguous
+    assert (h == 1 or not out._is_contiguous) and out.transpose(1, 2)._is_contiguous
     out.backward(dout.to(mojo))
     after = flash_ops.CALL_COUNTERS
     assert after["aten::_scaled_dot_product_flash_attention"] == before["aten::_scaled_dot_product_flash_attention"] + 1

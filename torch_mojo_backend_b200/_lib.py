@@ -38,6 +38,7 @@ EXPORTED_SYMBOLS = (
     "b200fa_bwd_simt",
     "b200fa_bwd_parts",
     "b200fa_strerror",
+    "b200fa_last_error_detail",
     "b200fa_version",
     "b200fa_launch_count",
 )
@@ -62,7 +63,8 @@ class Tensor4(ctypes.Structure):
 class B200FAError(RuntimeError):
     def __init__(self, code: int, where: str):
         self.code = code
-        super().__init__(f"{where}: {strerror(code)} (b200fa error {code})")
+        detail = load().b200fa_last_error_detail().decode() if code == ERR_CUDA else ""
+        super().__init__(f"{where}: {strerror(code)} (b200fa error {code})" + (f" [{detail}]" if detail else ""))
 
 
 _lib = None
@@ -98,6 +100,8 @@ def load() -> ctypes.CDLL:
     lib.b200fa_bwd_workspace_bytes.restype = ctypes.c_size_t
     lib.b200fa_strerror.argtypes = [ctypes.c_int]
     lib.b200fa_strerror.restype = ctypes.c_char_p
+    lib.b200fa_last_error_detail.argtypes = []
+    lib.b200fa_last_error_detail.restype = ctypes.c_char_p
     lib.b200fa_version.argtypes = []
     lib.b200fa_version.restype = ctypes.c_int
     lib.b200fa_launch_count.argtypes = []

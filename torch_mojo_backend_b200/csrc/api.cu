@@ -4,6 +4,7 @@
 // TMA descriptor encoding, kernel selection and launch accounting.
 #include <atomic>
 #include <cmath>
+#include <cstdio>
 #include <cstring>
 #include <mutex>
 
@@ -14,6 +15,13 @@ namespace b200fa {
 namespace {
 
 std::atomic<uint64_t> g_launches{0};
+
+// Text of the most recent CUDA failure seen by this thread (for b200fa_last_error_detail).
+thread_local char g_detail[256] = "";
+
+void note_cuda_error(const char* where, cudaError_t e) {
+  snprintf(g_detail, sizeof(g_detail), "%s: %s (%s)", where, cudaGetErrorName(e), cudaGetErrorString(e));
+}
 
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -60,7 +68,10 @@ struct DeviceGuard {
   bool ok = true;
   explicit DeviceGuard(int device) {
     if (cudaGetDevice(&prev) != cudaSuccess) { ok = false; return; }
-    if (device != prev && cudaSetDevice(device) != cudaSuccess) ok = false;
+    // Always set the device, even when it is already the current ordinal: a thread that has
+    // made no runtime call yet (the autograd engine's worker) has no context bound, and the
+    // driver-API tensor-map encode needs one.
+    if (cudaSetDevice(device) != cudaSuccess) ok = false;
   }
   ~DeviceGuard() {
     int cur = -1;
@@ -117,6 +128,8 @@ int b200fa_version(void) { return B200FA_VERSION; }
 
 uint64_t b200fa_launch_count(void) { return g_launches.load(); }
 
+const char* b200fa_last_error_detail(void) { return g_detail; }
+
 const char* b200fa_strerror(int code) {
   switch (code) {
     case B200FA_OK: return "ok";
@@ -163,13 +176,20 @@ static int fwd_impl(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200
   p.status = status_word;
 
   DeviceGuard guard(device);
-  if (!guard.ok) return B200FA_ERR_CUDA;
+  if (!guard.ok) {
+    note_cuda_error("cudaSetDevice", cudaGetLastError());
+    return B200FA_ERR_CUDA;
+  }
   if ((rc = check_device_is_sm100(device)) != B200FA_OK) return rc;
   int launches = 0;
+  // A stale error left on this thread by an earlier, unrelated runtime call must not be
+  // mistaken for a launch failure.
+  (void)cudaGetLastError();
   cudaError_t e = (dtype == kF32 || force_simt)
                       ? launch_fwd_simt(p, dtype, static_cast<cudaStream_t>(stream), &launches)
                       : launch_fwd_sm100(p, dtype, static_cast<cudaStream_t>(stream), &launches);
   g_launches += launches;
+  if (e != cudaSuccess) note_cuda_error("b200fa_fwd", e);
   return e == cudaSuccess ? B200FA_OK : B200FA_ERR_CUDA;
 }
 
@@ -240,13 +260,18 @@ static int bwd_impl(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200
   p.parts = parts;
 
   DeviceGuard guard(device);
-  if (!guard.ok) return B200FA_ERR_CUDA;
+  if (!guard.ok) {
+    note_cuda_error("cudaSetDevice", cudaGetLastError());
+    return B200FA_ERR_CUDA;
+  }
   if ((rc = check_device_is_sm100(device)) != B200FA_OK) return rc;
   int launches = 0;
+  (void)cudaGetLastError();
   cudaError_t e = (dtype == kF32 || force_simt)
                       ? launch_bwd_simt(p, dtype, static_cast<cudaStream_t>(stream), &launches)
                       : launch_bwd_sm100(p, dtype, static_cast<cudaStream_t>(stream), &launches);
   g_launches += launches;
+  if (e != cudaSuccess) note_cuda_error("b200fa_bwd", e);
   return e == cudaSuccess ? B200FA_OK : B200FA_ERR_CUDA;
 }
 

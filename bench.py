@@ -52,28 +52,70 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons through NVML while the timed region runs
+    (falls back to polling nvidia-smi when NVML bindings are unavailable)."""
 
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
         self.gpu_index = gpu_index
-        self.samples: list[list[str]] = []
+        self.clocks: list[float] = []
+        self.max_clock = None
+        self.reasons: set[str] = set()
         self._stop = threading.Event()
         self._thread = None
+        self._nvml = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = gpu_index
+            if visible:
+                entry = visible.split(",")[gpu_index].strip()
+                if entry.isdigit():
+                    phys = int(entry)
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_clock = float(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
+            self._nvml = pynvml
+        except Exception:
+            self._nvml = None
+
+    def _sample_nvml(self):
+        n = self._nvml
+        self.clocks.append(float(n.nvmlDeviceGetClockInfo(self._handle, n.NVML_CLOCK_SM)))
+        mask = n.nvmlDeviceGetCurrentClocksEventReasons(self._handle)
+        for name, bit in (("hw_slowdown", n.nvmlClocksEventReasonHwSlowdown),
+                          ("hw_thermal_slowdown", n.nvmlClocksEventReasonHwThermalSlowdown),
+                          ("sw_thermal_slowdown", n.nvmlClocksEventReasonSwThermalSlowdown),
+                          ("sw_power_cap", n.nvmlClocksEventReasonSwPowerCap)):
+            if mask & bit:
+                self.reasons.add(name)
+
+    def _sample_smi(self):
+        out = subprocess.run(
+            ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits"],
+            capture_output=True, text=True, timeout=5).stdout.strip()
+        if not out:
+            return
+        s = [x.strip() for x in out.splitlines()[0].split(",")]
+        self.clocks.append(float(s[0]))
+        self.max_clock = float(s[1])
+        for name, val in zip(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"], s[2:6]):
+            if val.lower().startswith("active"):
+                self.reasons.add(name)
 
     def _run(self):
         while not self._stop.is_set():
             try:
-                out = subprocess.run(
-                    ["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits"],
-                    capture_output=True, text=True, timeout=5).stdout.strip()
-                if out:
-                    self.samples.append([x.strip() for x in out.splitlines()[0].split(",")])
+                if self._nvml is not None:
+                    self._sample_nvml()
+                else:
+                    self._sample_smi()
             except Exception:
                 pass
-            self._stop.wait(0.1)
+            self._stop.wait(0.002 if self._nvml is not None else 0.1)
 
     def __enter__(self):
         self._thread = threading.Thread(target=self._run, daemon=True)
@@ -85,22 +127,13 @@ class ClockSampler:
         self._thread.join(timeout=10)
 
     def summary(self):
-        clocks, max_clocks, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for s in self.samples:
-            try:
-                clocks.append(float(s[0]))
-                max_clocks.append(float(s[1]))
-            except (ValueError, IndexError):
-                continue
-            for name, val in zip(names, s[2:6]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
         return {
-            "sm_mhz": statistics.median(clocks) if clocks else None,
-            "sm_max_mhz": max(max_clocks) if max_clocks else None,
-            "reasons": sorted(reasons),
-            "samples": len(clocks),
+            "sm_mhz": statistics.median(self.clocks) if self.clocks else None,
+            "sm_min_mhz": min(self.clocks) if self.clocks else None,
+            "sm_max_mhz": self.max_clock,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.clocks),
+            "source": "nvml" if self._nvml is not None else "nvidia-smi",
         }
 
 
@@ -199,7 +232,7 @@ def run_ours(args):
     value = world * step_flops / (ms_per_step * 1e-3) / 1e12
 
     # ---- end to end through the public operator API on the mojo device, host buffers in/out
-    e2e = run_e2e(cfg, rank, world, local, args)
+    e2e = None if args.no_e2e else run_e2e(cfg, rank, world, local, args)
 
     burst, sustained, peak_src = load_peaks()
     if do_bwd:
@@ -266,14 +299,20 @@ def run_e2e(cfg, rank, world, local, args):
 
     tmb.register_mojo_devices()
     torch.mojo.set_device(local)
-    host = [t.pin_memory() for t in O.make_inputs(cfg, seed=rank)]
+    cpu_inputs = O.make_inputs(cfg, seed=rank)
+    host = []
+    for t in cpu_inputs:
+        p = tmb.pinned_empty(t.shape, t.dtype)
+        p.copy_(t)
+        host.append(p)
     hq, hk, hv, hdo = host
     steps = max(1, min(args.steps, 5))
     gqa = cfg.Hq != cfg.Hkv
     h2d = sum(t.numel() * t.element_size() for t in ((hq, hk, hv, hdo) if cfg.backward else (hq, hk, hv)))
-    d2h = hq.numel() * hq.element_size()
-    if cfg.backward:
-        d2h += sum(t.numel() * t.element_size() for t in (hq, hk, hv))
+    # results land in pre-pinned host buffers: out, and dq/dk/dv when the config has a backward
+    res_out = tmb.pinned_empty(hq.shape, hq.dtype)
+    res_grads = [tmb.pinned_empty(t.shape, t.dtype) for t in (hq, hk, hv)] if cfg.backward else []
+    d2h = sum(t.numel() * t.element_size() for t in [res_out] + res_grads)
 
     def step():
         dev = torch.device("mojo", local)
@@ -286,11 +325,12 @@ def run_e2e(cfg, rank, world, local, args):
             do = hdo.to(dev, non_blocking=True)
         out = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=cfg.causal, scale=cfg.scale,
                                                                enable_gqa=gqa)
-        results = [out.detach().to("cpu", non_blocking=True)]
+        res_out.copy_(out.detach(), non_blocking=True)
         if cfg.backward:
             out.backward(do)
-            results += [t.grad.to("cpu", non_blocking=True) for t in (q, k, v)]
-        return results
+            for dst, t in zip(res_grads, (q, k, v)):
+                dst.copy_(t.grad, non_blocking=True)
+        return res_out
 
     for _ in range(2):
         step()
@@ -352,6 +392,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-sample-heads", type=int, default=2)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -39,9 +39,16 @@ def from_cuda(t: torch.Tensor):
     return TorchMojoTensor._from_cuda(t)
 
 
+def pinned_empty(shape, dtype: torch.dtype) -> torch.Tensor:
+    """A page-locked CPU tensor usable for non-blocking copies to and from mojo tensors."""
+    from .tensor import pinned_empty as _pinned_empty
+
+    return _pinned_empty(shape, dtype)
+
+
 def to_cuda(t) -> torch.Tensor:
     """Zero-copy: the CUDA tensor aliasing a mojo tensor's memory."""
     return t._cuda_view()
 
 
-__all__ = ["register_mojo_devices", "from_cuda", "to_cuda"]
+__all__ = ["register_mojo_devices", "from_cuda", "to_cuda", "pinned_empty"]

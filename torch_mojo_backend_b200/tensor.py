@@ -12,6 +12,7 @@ CUDA stream, and ``_ptr`` is a plain CUDA device address the C ABI consumes dire
 from __future__ import annotations
 
 import math
+import weakref
 
 import torch
 
@@ -38,6 +39,31 @@ def _compute_contiguous(shape, strides) -> bool:
             return False
         expected *= dim
     return True
+
+
+def _host_unregister(ptr: int) -> None:
+    try:
+        torch.cuda.cudart().cudaHostUnregister(ptr)
+    except Exception:
+        pass
+
+
+def pinned_empty(shape, dtype: torch.dtype) -> torch.Tensor:
+    """A page-locked CPU tensor for asynchronous transfers.
+
+    Once a PrivateUse1 backend is registered, ``torch.empty(pin_memory=True)`` and
+    ``Tensor.pin_memory()`` ask that backend for a pinned allocator, which a Python backend
+    cannot provide; this registers ordinary host memory with the CUDA driver instead.  The
+    registration is dropped when the returned tensor object is collected.
+    """
+    t = torch.empty(tuple(shape), dtype=dtype)
+    nbytes = t.numel() * t.element_size()
+    if nbytes:
+        rc = torch.cuda.cudart().cudaHostRegister(t.data_ptr(), nbytes, 0)
+        if int(rc) != 0:
+            raise RuntimeError(f"cudaHostRegister failed with error {int(rc)}")
+        weakref.finalize(t, _host_unregister, t.data_ptr())
+    return t
 
 
 def _alloc_holder(nbytes: int, index: int) -> torch.Tensor:
@@ -157,7 +183,7 @@ class TorchMojoTensor(torch.Tensor):
             return torch.empty(self._shape, dtype=self._dtype)
         src = self._cuda_view()
         if non_blocking:
-            dst = torch.empty(self._shape, dtype=self._dtype, pin_memory=True)
+            dst = pinned_empty(self._shape, self._dtype)
             dst.copy_(src, non_blocking=True)
             return dst
         return src.cpu()

@@ -97,6 +97,41 @@ int b200fa_bwd(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_te
                void* stream, int device, uint32_t* status_word);
 
 /*
+ * b200fa_bwd for callers that cannot allocate device memory.  (No counterpart in the
+ * reference, whose Python host allocates the scratch tensors itself.)
+ *
+ * Who needs it: a host that only passes through device pointers owned by some other runtime
+ * and has no CUDA allocator to ask for scratch; a backward that runs on a thread where the
+ * framework's allocator must not be re-entered; a serving loop that bans allocation once it
+ * is warm.  Instead of a workspace argument, the scratch (fp32 dQ accumulator and per-row
+ * statistics) lives in a fixed array compiled into the library, B200FA_NO_ALLOC_SCRATCH_BYTES
+ * (64 MiB) per GPU, held by every GPU that loads the library until the process exits.
+ *
+ *   - Problems whose b200fa_bwd_workspace_bytes(...) exceeds that size are refused with
+ *     B200FA_ERR_WORKSPACE (b200fa_last_error_detail() says how much was needed); nothing is
+ *     launched.  64 MiB covers e.g. B*Hq*S up to 245,760 rows at D=64 or 126,976 rows at
+ *     D=128 (GPT-2-small attention, B=8 H=12 S=1024 D=64, needs 26 MB).
+ *   - The call makes no cudaMalloc / cudaFree and calls no allocating routine.  The first
+ *     call on each device looks up the array's device address (cudaGetSymbolAddress with that
+ *     device current) and caches it; make that first call outside any stream capture.
+ *   - All calls on a device share the one array, and it keeps whatever the previous call
+ *     left there.  The kernels clear the part that must start at zero (the dQ accumulator)
+ *     themselves, on `stream`, before using it.  Because the array is shared, two calls whose
+ *     kernels can overlap on the GPU (different streams, or different host threads without
+ *     ordering between them) race on it: serialise them on one stream or with events.
+ *   - Inputs, outputs, return codes and numerics are those of b200fa_bwd.
+ */
+#define B200FA_NO_ALLOC_SCRATCH_BYTES (64u << 20)
+int b200fa_bwd_no_alloc(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_tensor4* v,
+                        const b200fa_tensor4* out, const b200fa_tensor4* dout, const float* lse,
+                        const b200fa_tensor4* dq, const b200fa_tensor4* dk, const b200fa_tensor4* dv,
+                        int dtype, int causal, float scale, void* stream, int device,
+                        uint32_t* status_word);
+
+/* B200FA_NO_ALLOC_SCRATCH_BYTES as the loaded library was built with. */
+size_t b200fa_no_alloc_scratch_bytes(void);
+
+/*
  * Same contracts as b200fa_fwd / b200fa_bwd, but always run the exact-fp32 SIMT kernels
  * whatever the storage type (16-bit inputs are widened to fp32 on load).  They exist so the
  * tensor-core kernels can be cross-checked on the device at sizes where a CPU comparison

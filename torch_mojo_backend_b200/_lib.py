@@ -37,6 +37,8 @@ EXPORTED_SYMBOLS = (
     "b200fa_fwd_simt",
     "b200fa_bwd_simt",
     "b200fa_bwd_parts",
+    "b200fa_bwd_no_alloc",
+    "b200fa_no_alloc_scratch_bytes",
     "b200fa_strerror",
     "b200fa_last_error_detail",
     "b200fa_version",
@@ -94,6 +96,11 @@ def load() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = bwd_args
         fn.restype = ctypes.c_int
+    # the no-alloc backward has b200fa_bwd's signature minus (workspace, workspace_bytes)
+    lib.b200fa_bwd_no_alloc.argtypes = bwd_args[:9] + bwd_args[11:]
+    lib.b200fa_bwd_no_alloc.restype = ctypes.c_int
+    lib.b200fa_no_alloc_scratch_bytes.argtypes = []
+    lib.b200fa_no_alloc_scratch_bytes.restype = ctypes.c_size_t
     lib.b200fa_bwd_parts.argtypes = bwd_args + [ctypes.c_int]
     lib.b200fa_bwd_parts.restype = ctypes.c_int
     lib.b200fa_bwd_workspace_bytes.argtypes = [ctypes.c_int64] * 5 + [ctypes.c_int]
@@ -152,3 +159,19 @@ def bwd(q: Tensor4, k: Tensor4, v: Tensor4, out: Tensor4, dout: Tensor4, lse_ptr
               ctypes.c_void_p(lse_ptr), ctypes.byref(dq), ctypes.byref(dk), ctypes.byref(dv),
               ctypes.c_void_p(workspace_ptr), ctypes.c_size_t(workspace_bytes), dtype, 1 if causal else 0,
               ctypes.c_float(scale), ctypes.c_void_p(stream), device, ctypes.c_void_p(status_ptr))
+
+
+def no_alloc_scratch_bytes() -> int:
+    return int(load().b200fa_no_alloc_scratch_bytes())
+
+
+def bwd_no_alloc(q: Tensor4, k: Tensor4, v: Tensor4, out: Tensor4, dout: Tensor4, lse_ptr: int, dq: Tensor4,
+                 dk: Tensor4, dv: Tensor4, dtype: int, causal: bool, scale: float, stream: int, device: int,
+                 status_ptr: int = 0) -> int:
+    """Backward for callers that cannot allocate: the scratch is the library's built-in device
+    array (see b200fa_bwd_no_alloc in include/b200fa.h).  The caller passes every input and
+    output; this wrapper allocates nothing either.  Returns the library's status code."""
+    return load().b200fa_bwd_no_alloc(
+        ctypes.byref(q), ctypes.byref(k), ctypes.byref(v), ctypes.byref(out), ctypes.byref(dout),
+        ctypes.c_void_p(lse_ptr), ctypes.byref(dq), ctypes.byref(dk), ctypes.byref(dv), dtype, 1 if causal else 0,
+        ctypes.c_float(scale), ctypes.c_void_p(stream), device, ctypes.c_void_p(status_ptr))

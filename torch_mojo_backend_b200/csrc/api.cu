@@ -303,4 +303,66 @@ int b200fa_bwd_simt(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200
                   device, status_word, true);
 }
 
+// ------------------------------------------------------------------------------------------
+// Backward without any caller-provided scratch: b200fa_bwd_no_alloc.
+//
+// Some hosts of this library own no CUDA allocator of their own and must not call one while
+// the backward runs: a runtime that hands over raw device pointers from its own pool (the
+// reference's MAX DeviceContext is one), an autograd engine thread whose allocator is locked
+// or already at its limit, or a serving loop that forbids allocation after warm-up.  For
+// them the three scratch arrays of the backward live in this fixed device array instead of
+// a workspace argument.  Every GPU that loads the library holds these bytes until the
+// process exits.
+// ------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_static_scratch[B200FA_NO_ALLOC_SCRATCH_BYTES];
+
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address:
+// the address each device gave the array is looked up once per device, with that device
+// current, and cached here.
+static void* g_static_scratch_addr[64] = {};
+static std::mutex g_static_scratch_mutex;
+
+static int static_scratch_for(int device, void** out) {
+  if (device < 0 || device >= 64) return B200FA_ERR_CUDA;
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (!g_static_scratch_addr[device]) {
+    DeviceGuard guard(device);
+    if (!guard.ok) {
+      note_cuda_error("cudaSetDevice", cudaGetLastError());
+      return B200FA_ERR_CUDA;
+    }
+    void* addr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&addr, g_static_scratch);
+    if (e != cudaSuccess || !addr) {
+      note_cuda_error("cudaGetSymbolAddress(g_static_scratch)", e);
+      return B200FA_ERR_CUDA;
+    }
+    g_static_scratch_addr[device] = addr;
+  }
+  *out = g_static_scratch_addr[device];
+  return B200FA_OK;
+}
+
+size_t b200fa_no_alloc_scratch_bytes(void) { return B200FA_NO_ALLOC_SCRATCH_BYTES; }
+
+int b200fa_bwd_no_alloc(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_tensor4* v,
+                        const b200fa_tensor4* out, const b200fa_tensor4* dout, const float* lse,
+                        const b200fa_tensor4* dq, const b200fa_tensor4* dk, const b200fa_tensor4* dv, int dtype,
+                        int causal, float scale, void* stream, int device, uint32_t* status_word) {
+  if (!q || !k) return B200FA_ERR_NULL;
+  const size_t need = b200fa_bwd_workspace_bytes(q->shape[0], q->shape[1], k->shape[1], q->shape[2], q->shape[3], dtype);
+  if (need > B200FA_NO_ALLOC_SCRATCH_BYTES) {
+    snprintf(g_detail, sizeof(g_detail),
+             "b200fa_bwd_no_alloc: this problem needs %zu bytes of scratch but the built-in scratch holds %zu; "
+             "use b200fa_bwd with a caller-provided workspace",
+             need, static_cast<size_t>(B200FA_NO_ALLOC_SCRATCH_BYTES));
+    return B200FA_ERR_WORKSPACE;
+  }
+  void* scratch = nullptr;
+  const int rc = static_scratch_for(device, &scratch);
+  if (rc != B200FA_OK) return rc;
+  return bwd_impl(q, k, v, out, dout, lse, dq, dk, dv, scratch, B200FA_NO_ALLOC_SCRATCH_BYTES, dtype, causal, scale,
+                  stream, device, status_word, false);
+}
+
 }  // extern "C"

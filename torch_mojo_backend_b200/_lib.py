@@ -14,7 +14,8 @@ import os
 from typing import Sequence
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libb200fa.so")
+# B200FA_LIB overrides the library path (used to try experimental builds)
+LIB_PATH = os.environ.get("B200FA_LIB") or os.path.join(_HERE, "libb200fa.so")
 
 F32, BF16, F16 = 0, 1, 2
 

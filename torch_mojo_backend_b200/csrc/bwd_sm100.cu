@@ -71,10 +71,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
   uint64_t* qdo_empty = do_full + Cfg::kStages;   // [kStages]
   uint64_t* s_full = qdo_empty + Cfg::kStages;    // S^T ready
   uint64_t* dp_full = s_full + 1;                 // dP^T ready
-  uint64_t* p_full = dp_full + 1;                 // P^T written (256 arrivals)
-  uint64_t* ds_full = p_full + 1;                 // dS^T written (256 arrivals)
+  uint64_t* p_full = dp_full + 1;                 // P^T written (8 warp arrivals)
+  uint64_t* ds_full = p_full + 1;                 // dS^T written (8 warp arrivals)
   uint64_t* dq_full = ds_full + 1;                // dQ tile ready
-  uint64_t* dq_empty = dq_full + 1;               // dQ tile drained (128 arrivals)
+  uint64_t* dq_empty = dq_full + 1;               // dQ tile drained (4 warp arrivals)
   uint64_t* dkdv_full = dq_empty + 1;             // everything accumulated
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dkdv_full + 1);
   volatile uint32_t* abort_flag = tmem_slot + 1;
@@ -106,10 +106,11 @@ bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
     }
     mbar_init(s_full, 1);
     mbar_init(dp_full, 1);
-    mbar_init(p_full, 256);
-    mbar_init(ds_full, 256);
+    // one elected arrival per warp: 8 compute warps, 4 drain warps
+    mbar_init(p_full, 8);
+    mbar_init(ds_full, 8);
     mbar_init(dq_full, 1);
-    mbar_init(dq_empty, 128);
+    mbar_init(dq_empty, 4);
     mbar_init(dkdv_full, 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -176,7 +177,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(p_full);
+      mbar_arrive_warp(p_full);
       // ---- dS^T = P^T * (dP^T - dpsum)
       B200FA_WAIT(dp_full, i & 1, 0x510);
       B200FA_WAIT(&do_full[stage], (i / Cfg::kStages) & 1, 0x511);
@@ -206,7 +207,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
       tmem_wait_st();
       tc_fence_before();
       fence_proxy_async_smem();
-      mbar_arrive(ds_full);
+      mbar_arrive_warp(ds_full);
     }
     // ---- epilogue: dV and dK (this warpgroup's half of the head dimension)
     B200FA_WAIT(dkdv_full, 0, 0x520);
@@ -268,7 +269,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
         if (ch == kD / 32 - 1) {
           // every column is in registers: the accumulator columns may be overwritten
           tc_fence_before();
-          mbar_arrive(dq_empty);
+          mbar_arrive_warp(dq_empty);
         }
         const float* af = reinterpret_cast<const float*>(a);
 #pragma unroll
@@ -284,64 +285,72 @@ bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
         constexpr uint32_t idesc_st = umma_idesc(kBf16, false, false, 128, 128);  // S^T, dP^T
         constexpr uint32_t idesc_acc = umma_idesc(kBf16, false, true, 128, kD);   // dV, dK (A from TMEM)
         constexpr uint32_t idesc_dq = umma_idesc(kBf16, true, true, 128, kD);     // dQ (A, B MN-major)
-        const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), aDO = smem_u32(sDO),
-                       aDS = smem_u32(sDS);
         const uint32_t tS = tmem_base + Cfg::kTmemS, tDP = tmem_base + Cfg::kTmemDP,
                        tDV = tmem_base + Cfg::kTmemDV, tDK = tmem_base + Cfg::kTmemDK,
                        tDQ = tmem_base + Cfg::kTmemDQ;
+        // Descriptors: fixed high word + start-address low word; K-major form (LBO unused) for
+        // the S^T / dP^T operands, MN-major form (LBO = next 64-column sub-tile) for the rest.
+        const UmmaDesc kK = umma_desc_split(smem_u32(sK), 16, 1024), kV = umma_desc_split(smem_u32(sV), 16, 1024),
+                       kQ = umma_desc_split(smem_u32(sQ), 16, 1024), kDO = umma_desc_split(smem_u32(sDO), 16, 1024);
+        const UmmaDesc mK = umma_desc_split(smem_u32(sK), kSubTileBytes, 1024),
+                       mQ = umma_desc_split(smem_u32(sQ), kSubTileBytes, 1024),
+                       mDO = umma_desc_split(smem_u32(sDO), kSubTileBytes, 1024),
+                       mDS = umma_desc_split(smem_u32(sDS), kSubTileBytes, 1024);
         // D[128 x 128] = A[128 x kD] * B[128 x kD]^T, both K-major
-        auto issue_kmajor = [&](uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr) {
+        auto issue_kmajor = [&](uint32_t d_tmem, const UmmaDesc& a, const UmmaDesc& b, uint32_t b_stage_lo) {
 #pragma unroll
           for (int kk = 0; kk < kD / 16; ++kk) {
-            const uint32_t off = (kk >> 2) * kSubTileBytes + (kk & 3) * 32;
-            umma_ss(d_tmem, umma_smem_desc(a_addr + off, 16, 1024), umma_smem_desc(b_addr + off, 16, 1024),
-                    idesc_st, kk > 0);
+            const uint32_t off = umma_off((kk >> 2) * kSubTileBytes + (kk & 3) * 32);
+            if (kk == 0) umma_ss_fast<false>(d_tmem, a.lo + off, a.hi, b.lo + b_stage_lo + off, b.hi, idesc_st);
+            else         umma_ss_fast<true>(d_tmem, a.lo + off, a.hi, b.lo + b_stage_lo + off, b.hi, idesc_st);
           }
         };
         // D[128 x kD] (+)= A^T-in-TMEM[128 x 128] * B[128 x kD] (B rows are the contraction index)
-        auto issue_ts = [&](uint32_t d_tmem, uint32_t a_tmem, uint32_t b_addr, bool acc) {
+        auto issue_ts = [&](uint32_t d_tmem, uint32_t a_tmem, const UmmaDesc& b, uint32_t b_stage_lo, bool acc) {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
             const uint32_t a_col = (kk < 4) ? kk * 8 : 64 + (kk - 4) * 8;
-            umma_ts(d_tmem, a_tmem + a_col, umma_smem_desc(b_addr + kk * 2048, kSubTileBytes, 1024), idesc_acc,
-                    (acc || kk > 0) ? 1u : 0u);
+            const uint32_t b_lo = b.lo + b_stage_lo + umma_off(kk * 2048);
+            if (kk == 0 && !acc) umma_ts_fast<false>(d_tmem, a_tmem + a_col, b_lo, b.hi, idesc_acc);
+            else                 umma_ts_fast<true>(d_tmem, a_tmem + a_col, b_lo, b.hi, idesc_acc);
           }
         };
         B200FA_WAIT(kv_full, 0, 0x700);
         B200FA_WAIT(&q_full[0], 0, 0x701);
         tc_fence_after();
-        issue_kmajor(tS, aK, aQ);
+        issue_kmajor(tS, kK, kQ, 0);
         umma_commit(s_full);
         B200FA_WAIT(&do_full[0], 0, 0x702);
         tc_fence_after();
-        issue_kmajor(tDP, aV, aDO);
+        issue_kmajor(tDP, kV, kDO, 0);
         umma_commit(dp_full);
         for (int i = 0; i < steps; ++i) {
           const int stage = i % Cfg::kStages;
-          const uint32_t q_addr = aQ + stage * Cfg::kTileBytes;
-          const uint32_t do_addr = aDO + stage * Cfg::kTileBytes;
+          const uint32_t stage_lo = stage * umma_off(Cfg::kTileBytes);
           const bool has_next = (i + 1 < steps);
           const int nstage = (i + 1) % Cfg::kStages;
+          const uint32_t nstage_lo = nstage * umma_off(Cfg::kTileBytes);
           const uint32_t nphase = static_cast<uint32_t>(((i + 1) / Cfg::kStages) & 1);
           // dV += P^T dO
           B200FA_WAIT(p_full, i & 1, 0x710);
           tc_fence_after();
-          issue_ts(tDV, tS, do_addr, i > 0);
+          issue_ts(tDV, tS, mDO, stage_lo, i > 0);
           // S^T of the next step can start as soon as P^T has been consumed (in issue order)
           if (has_next) {
             B200FA_WAIT(&q_full[nstage], nphase, 0x711);
             tc_fence_after();
-            issue_kmajor(tS, aK, aQ + nstage * Cfg::kTileBytes);
+            issue_kmajor(tS, kK, kQ, nstage_lo);
             umma_commit(s_full);
           }
           // dK += dS^T Q ; dQ = dS K
           B200FA_WAIT(ds_full, i & 1, 0x712);
           tc_fence_after();
-          issue_ts(tDK, tDP, q_addr, i > 0);
+          issue_ts(tDK, tDP, mQ, stage_lo, i > 0);
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
-            umma_ss(tDQ, umma_smem_desc(aDS + kk * 2048, kSubTileBytes, 1024),
-                    umma_smem_desc(aK + kk * 2048, kSubTileBytes, 1024), idesc_dq, kk > 0);
+            const uint32_t off = umma_off(kk * 2048);
+            if (kk == 0) umma_ss_fast<false>(tDQ, mDS.lo + off, mDS.hi, mK.lo + off, mK.hi, idesc_dq);
+            else         umma_ss_fast<true>(tDQ, mDS.lo + off, mDS.hi, mK.lo + off, mK.hi, idesc_dq);
           }
           umma_commit(dq_full);
           umma_commit(&qdo_empty[stage]);
@@ -349,7 +358,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
             B200FA_WAIT(&do_full[nstage], nphase, 0x713);
             B200FA_WAIT(dq_empty, i & 1, 0x714);
             tc_fence_after();
-            issue_kmajor(tDP, aV, aDO + nstage * Cfg::kTileBytes);
+            issue_kmajor(tDP, kV, kDO, nstage_lo);
             umma_commit(dp_full);
           }
         }

@@ -11,14 +11,31 @@
 //   warps 0-3   softmax of query tile 0   (thread i <-> TMEM lane i <-> query row i)
 //   warps 4-7   softmax of query tile 1
 //   warps 8-11  correction: rescale O in TMEM when a row max moved, final O/l + LSE epilogue
-//   warp  12    MMA issuer (one elected lane issues every tcgen05.mma / commit)
-//   warp  13    TMA producer (Q once, then a ring of K/V tiles)
-//   warps 14-15 idle (they only donate registers)
+//   warps 12-13 MMA issuers, one per query tile (one elected lane each issues tcgen05.mma / commit)
+//   warp  14    TMA producer (Q once, then a ring of K/V tiles)
+//   warp  15    idle (it only donates registers)
 //
 // TMEM columns: S0 | S1 | O0 | O1.  P (16-bit, two per column) overwrites the first half of
 // its own S columns and is consumed as the TMEM A-operand of the P V MMA.
 #include "common.cuh"
 #include "ptx.cuh"
+
+#ifndef B200FA_ABL
+#define B200FA_ABL 0
+#endif
+
+#ifdef B200FA_TRACE
+// debug timeline: role r appends (event, clock) records for CTA 0 into the buffer behind the status word
+#define TRACE(role, ev)                                                                          \
+  do {                                                                                           \
+    if (p.status != nullptr && blockIdx.x == 0 && (threadIdx.x & 31) == 0 && trace_n < 2000) {                          \
+      reinterpret_cast<unsigned long long*>(p.status + 16)[(role) * 2048 + trace_n++] =          \
+          (static_cast<unsigned long long>(clock64()) << 8) | (ev);                              \
+    }                                                                                            \
+  } while (0)
+#else
+#define TRACE(role, ev) do {} while (0)
+#endif
 
 namespace b200fa {
 namespace {
@@ -28,13 +45,38 @@ constexpr int kBN = 128;        // key rows per tile
 constexpr int kThreads = 512;
 constexpr int kSubTileBytes = 128 * 128;  // one 128-row x 64-column (128 B) swizzled box
 
+// Lazy rescaling threshold (log2 domain): O and l are only rescaled when the running row
+// maximum grows by more than this, so P can be as large as 2^8 against a stale maximum.
+constexpr float kRescaleLog2 = 8.f;
+// Of every 8 column pairs, this many take their exponentials on the FMA pipe (range
+// reduction + cubic) instead of the MUFU unit, which would otherwise cap the kernel.
+constexpr int kEmuOf8 = 3;
+
+// 2^x for x <= ~127 on the FMA pipe, two values at a time: x = n + f with n = floor(x),
+// 2^f by a cubic fitted on [0,1) (max relative error 8.7e-5, far below 16-bit rounding of
+// P), and n added straight into the exponent field.
+__device__ __forceinline__ float2 exp2_emulated2(float2 x) {
+  const float kMagic = 12582912.f;  // 1.5 * 2^23: x + kMagic (rounded down) holds floor(x) in its low mantissa bits
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const float2 xi = __fadd2_rd(x, make_float2(kMagic, kMagic));
+  const float2 fl = __fadd2_rn(xi, make_float2(-kMagic, -kMagic));
+  const float2 f = __fadd2_rn(x, make_float2(-fl.x, -fl.y));
+  float2 r = __ffma2_rn(make_float2(0.07705805f, 0.07705805f), f, make_float2(0.22764558f, 0.22764558f));
+  r = __ffma2_rn(r, f, make_float2(0.69512289f, 0.69512289f));
+  r = __ffma2_rn(r, f, make_float2(1.f, 1.f));
+  r.x = __int_as_float(__float_as_int(r.x) + (__float_as_int(xi.x) << 23));
+  r.y = __int_as_float(__float_as_int(r.y) + (__float_as_int(xi.y) << 23));
+  return r;
+}
+
 template <int kD>
 struct FwdCfg {
   static constexpr int kTileBytes = kBM * kD * 2;
   static constexpr int kSub = kD / 64;                  // 64-column boxes per tile
   static constexpr int kStages = (kD == 128) ? 4 : 8;   // K/V ring slots
   static constexpr int kTmemS0 = 0, kTmemS1 = 128, kTmemO0 = 256, kTmemO1 = 256 + kD;
-  static constexpr int kNumBars = 2 + 2 * kStages + 12;
+  static constexpr int kNumBars = 2 + 2 * kStages + 16;
   static constexpr int kSmemBytes = 1024 /*align slack*/ + 2 * kTileBytes + kStages * kTileBytes +
                                     4 * 128 * 4 /*msg+max*/ + kNumBars * 8 + 64;
 };
@@ -61,16 +103,20 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
   uint64_t* kv_full = q_full + 2;               // [kStages]
   uint64_t* kv_empty = kv_full + Cfg::kStages;  // [kStages]
   uint64_t* s_full = kv_empty + Cfg::kStages;   // [2]
-  uint64_t* p_full = s_full + 2;                // [2]
-  uint64_t* o_full = p_full + 2;                // [2]
+  uint64_t* p_full = s_full + 2;                // [2 tiles][2 halves of the KV columns]
+  uint64_t* o_full = p_full + 4;                // [2]
   uint64_t* o_ready = o_full + 2;               // [2]
   uint64_t* sc_full = o_ready + 2;              // [2]
   uint64_t* sc_empty = sc_full + 2;             // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sc_empty + 2);
+  uint64_t* turn = sc_empty + 2;                // [2] MMA issuers' turn-taking
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(turn + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+#ifdef B200FA_TRACE
+  int trace_n = 0;
+#endif
 
   // ---- which (pair, head, batch) this CTA owns: head groups keep K/V in L2, and inside a
   // group the heaviest (latest) causal pairs are scheduled first.
@@ -109,15 +155,18 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
     mbar_init(&q_full[1], 1);
     for (int i = 0; i < Cfg::kStages; ++i) {
       mbar_init(&kv_full[i], 1);
-      mbar_init(&kv_empty[i], 1);
+      mbar_init(&kv_empty[i], 2);  // released by both query tiles' MMA issuers
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(&s_full[t], 1);
-      mbar_init(&p_full[t], 128);
+      // fed by four warps each, one elected arrival per warp
+      mbar_init(&p_full[t * 2], 8);      // 4 softmax warps (P half 0) + 4 correction warps (O ready)
+      mbar_init(&p_full[t * 2 + 1], 4);
       mbar_init(&o_full[t], 1);
-      mbar_init(&o_ready[t], 128);
-      mbar_init(&sc_full[t], 128);
-      mbar_init(&sc_empty[t], 128);
+      mbar_init(&o_ready[t], 4);         // unused: "O ready" is folded into p_full[t][0]
+      mbar_init(&sc_full[t], 4);
+      mbar_init(&sc_empty[t], 4);
+      mbar_init(&turn[t], 1);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -127,7 +176,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
-  if (warp == 13 && lane == 0) {
+  if (warp == 14 && lane == 0) {
     tma_prefetch_desc(&mapQ);
     tma_prefetch_desc(&mapK);
     tma_prefetch_desc(&mapV);
@@ -142,7 +191,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
 
   if (warp < 8) {
     // =========================== softmax warps ===========================
-    reg_alloc<184>();
+    reg_alloc<176>();
     const int t = warp >> 2;
     const int row = threadIdx.x & 127;
     const int nblk = n_t[t];
@@ -150,17 +199,27 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
     const uint32_t tS = tmem_base + lane_off + (t == 0 ? Cfg::kTmemS0 : Cfg::kTmemS1);
     const float c = p.scale_log2;
     const int q_row = row0 + t * kBM + row;  // global query row
+    // m: the row maximum the exponentials are taken against.  It is only raised when the
+    // true maximum has grown by more than 2^kRescaleLog2 (lazy rescaling), so most KV
+    // tiles need no correction of O; l is the row sum relative to that same m.
     float m = -INFINITY, l = 0.f;
     for (int j = 0; j < nblk; ++j) {
       B200FA_WAIT(&s_full[t], j & 1, 0x100 + t);
       tc_fence_after();
+      if ((warp & 3) == 0) TRACE(t, 1);
       uint32_t s[128];
-      tmem_ld32(tS + 0, s + 0);
-      tmem_ld32(tS + 32, s + 32);
-      tmem_ld32(tS + 64, s + 64);
-      tmem_ld32(tS + 96, s + 96);
-      tmem_wait_ld();
+      if (B200FA_ABL & 16) {
+#pragma unroll
+        for (int i = 0; i < 128; ++i) s[i] = __float_as_uint(0.001f * (i + row));
+      } else {
+        tmem_ld32(tS + 0, s + 0);
+        tmem_ld32(tS + 32, s + 32);
+        tmem_ld32(tS + 64, s + 64);
+        tmem_ld32(tS + 96, s + 96);
+        tmem_wait_ld();
+      }
       float* sf = reinterpret_cast<float*>(s);
+      if ((warp & 3) == 0) TRACE(t, 2);
       const int col0 = j * kBN;
       // mask: causal diagonal tile and/or columns beyond Sk
       const bool need_mask = (kCausal && (col0 + kBN - 1 > row0 + t * kBM)) || (col0 + kBN > p.Sk);
@@ -171,41 +230,65 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
           if (col0 + i > limit) sf[i] = -INFINITY;
         }
       }
-      float mx = sf[0];
+      // row max, four independent chains
+      float mx0 = sf[0], mx1 = sf[1], mx2 = sf[2], mx3 = sf[3];
 #pragma unroll
-      for (int i = 1; i < 128; ++i) mx = fmaxf(mx, sf[i]);
-      float m_new = fmaxf(m, mx);
+      for (int i = 4; i < ((B200FA_ABL & 2) ? 8 : 128); i += 4) {
+        mx0 = fmaxf(mx0, sf[i]);
+        mx1 = fmaxf(mx1, sf[i + 1]);
+        mx2 = fmaxf(mx2, sf[i + 2]);
+        mx3 = fmaxf(mx3, sf[i + 3]);
+      }
+      float m_new = fmaxf(fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)), m);
       // rows past the end of the sequence (or fully masked) must not produce NaN
       if (m_new == -INFINITY) m_new = 0.f;
-      const float sc = ex2_approx((m - m_new) * c);
+      float sc = 1.f;
+      if ((m_new - m) * c > kRescaleLog2) {  // always true on the first tile (m = -inf)
+        sc = ex2_approx((m - m_new) * c);
+        m = m_new;
+      }
       if (j > 0) {
         B200FA_WAIT(&sc_empty[t], (j - 1) & 1, 0x110 + t);
       }
       sMsg[t * 128 + row] = sc;
-      mbar_arrive(&sc_full[t]);
-      m = m_new;
+      mbar_arrive_warp(&sc_full[t]);
+      if ((warp & 3) == 0) TRACE(t, 3);
       const float mc = m * c;
-      float rs = 0.f;
+      const float2 c2 = make_float2(c, c);
+      const float2 nmc2 = make_float2(-mc, -mc);
+      float2 rsa = make_float2(0.f, 0.f), rsb = make_float2(0.f, 0.f);
       uint32_t pk[64];
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        const float p0 = ex2_approx(fmaf(sf[2 * i], c, -mc));
-        const float p1 = ex2_approx(fmaf(sf[2 * i + 1], c, -mc));
-        rs += p0 + p1;
-        pk[i] = pack2<kBf16>(p0, p1);
+      for (int half = 0; half < 2; ++half) {
+#pragma unroll
+        for (int i = half * 32; i < half * 32 + 32; ++i) {
+          const float2 x = __ffma2_rn(make_float2(sf[2 * i], sf[2 * i + 1]), c2, nmc2);
+          float2 pv;
+          if (B200FA_ABL & 1) {
+            pv = x;
+          } else if ((i & 7) < kEmuOf8) {
+            pv = exp2_emulated2(x);
+          } else {
+            pv = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+          }
+          if (i & 1) rsb = __fadd2_rn(rsb, pv); else rsa = __fadd2_rn(rsa, pv);
+          pk[i] = pack2<kBf16>(pv.x, pv.y);
+        }
+        if (!(B200FA_ABL & 8)) {
+          tmem_st32(tS + half * 32, pk + half * 32);
+          tmem_wait_st();
+        }
+        tc_fence_before();
+        mbar_arrive_warp(&p_full[t * 2 + half]);
+        if ((warp & 3) == 0) TRACE(t, 4 + half);
       }
-      tmem_st32(tS + 0, pk + 0);
-      tmem_st32(tS + 32, pk + 32);
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(&p_full[t]);
-      l = l * sc + rs;
+      l = l * sc + ((rsa.x + rsa.y) + (rsb.x + rsb.y));
     }
     if (nblk > 0) {
       B200FA_WAIT(&sc_empty[t], (nblk - 1) & 1, 0x120 + t);
       sMsg[t * 128 + row] = l;
       sMax[t * 128 + row] = m;
-      mbar_arrive(&sc_full[t]);
+      mbar_arrive_warp(&sc_full[t]);
     }
   } else if (warp < 12) {
     // =========================== correction warps ===========================
@@ -220,7 +303,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
       if (!mbar_wait(&sc_full[t], nblk & 1, abort_flag, p.status, 0x200 + t)) return false;
       const float l = sMsg[t * 128 + row];
       const float m = sMax[t * 128 + row];
-      if (!mbar_wait(&o_full[t], (nblk - 1) & 1, abort_flag, p.status, 0x210 + t)) return false;
+      if (!mbar_wait(&o_full[t], 0, abort_flag, p.status, 0x210 + t)) return false;
       tc_fence_after();
       const float inv_l = 1.f / l;
       const int q_row = row0 + t * kBM + row;
@@ -257,10 +340,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
       for (int t = 0; t < 2; ++t) {
         if (j < n_t[t]) {
           B200FA_WAIT(&sc_full[t], j & 1, 0x220 + t);
+          if (warp == 8) TRACE(2, 10 + t);
           const float sc = sMsg[t * 128 + row];
-          mbar_arrive(&sc_empty[t]);
+          mbar_arrive_warp(&sc_empty[t]);
           if (j > 0) {
-            B200FA_WAIT(&o_full[t], (j - 1) & 1, 0x230 + t);
+            // Q K^T of tile j was issued after P V of tile j-1, so its commit covers both
+            B200FA_WAIT(&s_full[t], j & 1, 0x230 + t);
             tc_fence_after();
             if (__any_sync(0xffffffffu, sc != 1.f)) {
               const uint32_t tO = tmem_base + lane_off + (t == 0 ? Cfg::kTmemO0 : Cfg::kTmemO1);
@@ -278,7 +363,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
             }
             tc_fence_before();
           }
-          mbar_arrive(&o_ready[t]);
+          mbar_arrive_warp(&p_full[t * 2]);
+          if (warp == 8) TRACE(2, 12 + t);
         }
       }
       // a tile that just saw its last KV block can be finished while the other still runs
@@ -291,75 +377,131 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
     }
     if (!epilogue(1)) goto teardown;
   } else {
-    reg_dealloc<56>();
-    if (warp == 12) {
-      // =========================== MMA issuer ===========================
-      if (lane == 0) {
+    reg_dealloc<72>();
+    if (warp == 12 || warp == 13) {
+      // =========================== MMA issuers (one per query tile) ===========================
+      // A tcgen05.mma only issues once the tensor pipe has room, so the issuing lane is stalled
+      // for about as long as its MMAs run, and every wait or commit it executes in between is
+      // time the pipe could drain.  Giving each query tile its own issuing lane lets one
+      // lane's waits overlap the other lane's MMAs.
+      const int t = warp - 12;
+      const int nblk = n_t[t];
+      if (lane == 0 && nblk > 0) {
         constexpr uint32_t idesc_qk = umma_idesc(kBf16, false, false, 128, 128);
         constexpr uint32_t idesc_pv = umma_idesc(kBf16, false, true, 128, kD);
-        const uint32_t sQ_addr = smem_u32(sQ);
-        const uint32_t sKV_addr = smem_u32(sKV);
-        const uint32_t tS[2] = {tmem_base + Cfg::kTmemS0, tmem_base + Cfg::kTmemS1};
-        const uint32_t tO[2] = {tmem_base + Cfg::kTmemO0, tmem_base + Cfg::kTmemO1};
-        auto issue_qk = [&](int t, uint32_t k_addr) {
-          const uint32_t q_addr = sQ_addr + t * Cfg::kTileBytes;
+        const uint32_t tS = tmem_base + (t == 0 ? Cfg::kTmemS0 : Cfg::kTmemS1);
+        const uint32_t tO = tmem_base + (t == 0 ? Cfg::kTmemO0 : Cfg::kTmemO1);
+        // descriptors are a fixed high word plus a start-address word; stepping along the
+        // contraction dimension or to another ring slot only adds to the low word
+        const UmmaDesc dQ = umma_desc_split(smem_u32(sQ) + t * Cfg::kTileBytes, 16, 1024);  // K-major Q tile
+        const UmmaDesc dK = umma_desc_split(smem_u32(sKV), 16, 1024);             // ring slot as K-major K
+        const UmmaDesc dV = umma_desc_split(smem_u32(sKV), kSubTileBytes, 1024);  // ring slot as MN-major V
+        auto issue_qk = [&](uint32_t slot_lo) {
 #pragma unroll
           for (int kk = 0; kk < kD / 16; ++kk) {
-            const uint32_t off = (kk >> 2) * kSubTileBytes + (kk & 3) * 32;
-            umma_ss(tS[t], umma_smem_desc(q_addr + off, 16, 1024), umma_smem_desc(k_addr + off, 16, 1024),
-                    idesc_qk, kk > 0);
+            const uint32_t off = umma_off((kk >> 2) * kSubTileBytes + (kk & 3) * 32);
+            if (kk == 0) umma_ss_fast<false>(tS, dQ.lo + off, dQ.hi, dK.lo + slot_lo + off, dK.hi, idesc_qk);
+            else         umma_ss_fast<true>(tS, dQ.lo + off, dQ.hi, dK.lo + slot_lo + off, dK.hi, idesc_qk);
           }
         };
-        auto issue_pv = [&](int t, uint32_t v_addr, bool acc) {
+        // half 0: KV rows 0-63 of the tile, half 1: rows 64-127 (P arrives in two halves)
+        auto issue_pv = [&](uint32_t slot_lo, bool first, int half) {
 #pragma unroll
-          for (int kk = 0; kk < kBN / 16; ++kk) {
-            umma_ts(tO[t], tS[t] + kk * 8, umma_smem_desc(v_addr + kk * 2048, kSubTileBytes, 1024), idesc_pv,
-                    (acc || kk > 0) ? 1u : 0u);
+          for (int kq = 0; kq < 4; ++kq) {
+            const int kk = half * 4 + kq;
+            const uint32_t b_lo = dV.lo + slot_lo + umma_off(kk * 2048);
+            if (kk == 0 && first) umma_ts_fast<false>(tO, tS + kk * 8, b_lo, dV.hi, idesc_pv);
+            else                  umma_ts_fast<true>(tO, tS + kk * 8, b_lo, dV.hi, idesc_pv);
           }
         };
-        auto slot_addr = [&](int seq) { return sKV_addr + (seq % Cfg::kStages) * Cfg::kTileBytes; };
-        auto slot_phase = [&](int seq) { return static_cast<uint32_t>((seq / Cfg::kStages) & 1); };
-        if (n_max > 0) {
-          // prologue: S_t = Q_t K_0^T
-          B200FA_WAIT(&kv_full[0], 0, 0x300);
-          for (int t = 0; t < 2; ++t) {
-            if (n_t[t] > 0) {
-              B200FA_WAIT(&q_full[t], 0, 0x301 + t);
-              tc_fence_after();
-              issue_qk(t, slot_addr(0));
-              umma_commit(&s_full[t]);
-            }
+        // The two issuing lanes take turns: a lane issues one block of MMAs (P V of the
+        // current KV tile, then Q K^T of the next) only while it holds the turn, and hands it
+        // over before it commits.  That keeps the two query tiles in anti-phase - one tile's
+        // MMAs run while the other tile is in softmax - instead of drifting into lockstep.
+        // turn[t] completes once per block of the OTHER lane; lane 0 opens.
+        int turn_k = 0;
+        auto take_turn = [&]() -> bool {
+          bool ok = true;
+          if (t == 1) ok = mbar_wait(&turn[1], turn_k & 1, abort_flag, p.status, 0x370);
+          else if (turn_k > 0) ok = mbar_wait(&turn[0], (turn_k - 1) & 1, abort_flag, p.status, 0x371);
+          ++turn_k;
+          return ok;
+        };
+        // block 0: S_t = Q_t K_0^T
+        B200FA_WAIT(&q_full[t], 0, 0x301 + t);
+        B200FA_WAIT(&kv_full[0], 0, 0x300);
+        if (!take_turn()) goto teardown;
+        tc_fence_after();
+        issue_qk(0);
+        mbar_arrive(&turn[1 - t]);
+        umma_commit(&s_full[t]);
+        umma_commit(&kv_empty[0]);
+        int slot = 1;         // ring slot of V_j; K_{j+1} follows in the next slot
+        uint32_t phase = 0;   // parity of the ring pass V_j's slot is in
+        for (int j = 0; j < nblk; ++j) {
+          const int vslot = slot;
+          const uint32_t vphase = phase;
+          if (++slot == Cfg::kStages) { slot = 0; phase ^= 1; }
+          const bool has_next = (j + 1 < nblk);
+          // everything that can be waited for without holding the turn
+          B200FA_WAIT(&kv_full[vslot], vphase, 0x310);
+          if (has_next) { B200FA_WAIT(&kv_full[slot], phase, 0x340); }
+          B200FA_WAIT(&p_full[t * 2], j & 1, 0x320 + t);  // P half 0 written and O ready
+          if (!take_turn()) goto teardown;
+          tc_fence_after();
+          TRACE(3 + t, 24);
+          issue_pv(vslot * umma_off(Cfg::kTileBytes), j == 0, 0);
+          B200FA_WAIT(&p_full[t * 2 + 1], j & 1, 0x324 + t);
+          tc_fence_after();
+          TRACE(3 + t, 26);
+          issue_pv(vslot * umma_off(Cfg::kTileBytes), false, 1);
+          if (has_next) issue_qk(slot * umma_off(Cfg::kTileBytes));
+          mbar_arrive(&turn[1 - t]);
+          TRACE(3 + t, 30);
+          if (has_next) {
+            // also tells the correction warps that P V of tile j has completed
+            umma_commit(&s_full[t]);
+            umma_commit(&kv_empty[slot]);
+          } else {
+            umma_commit(&o_full[t]);
           }
-          umma_commit(&kv_empty[0]);
-          for (int j = 0; j < n_max; ++j) {
-            const int vseq = 2 * j + 1, kseq = 2 * j + 2;
-            B200FA_WAIT(&kv_full[vseq % Cfg::kStages], slot_phase(vseq), 0x310);
-            const bool has_next = (j + 1 < n_max);
-            bool k_ready = false;
-            for (int t = 0; t < 2; ++t) {
-              if (j < n_t[t]) {
-                B200FA_WAIT(&p_full[t], j & 1, 0x320 + t);
-                B200FA_WAIT(&o_ready[t], j & 1, 0x330 + t);
-                tc_fence_after();
-                issue_pv(t, slot_addr(vseq), j > 0);
-                umma_commit(&o_full[t]);
-                if (j + 1 < n_t[t]) {
-                  if (!k_ready) {
-                    B200FA_WAIT(&kv_full[kseq % Cfg::kStages], slot_phase(kseq), 0x340);
-                    tc_fence_after();
-                    k_ready = true;
-                  }
-                  issue_qk(t, slot_addr(kseq));
-                  umma_commit(&s_full[t]);
-                }
-              }
-            }
-            umma_commit(&kv_empty[vseq % Cfg::kStages]);
-            if (has_next) umma_commit(&kv_empty[kseq % Cfg::kStages]);
+          umma_commit(&kv_empty[vslot]);
+          if (++slot == Cfg::kStages) { slot = 0; phase ^= 1; }
+        }
+        // KV tiles only the other query tile visits still need this tile's release, and the
+        // other lane still needs its turns
+        for (int j = nblk; j < n_max; ++j) {
+          // K_j sits in the slot before V_j; slot/phase currently point at V_j
+          const int kslot = (slot == 0) ? Cfg::kStages - 1 : slot - 1;
+          const uint32_t kphase = (slot == 0) ? (phase ^ 1) : phase;
+          B200FA_WAIT(&kv_full[kslot], kphase, 0x350);
+          mbar_arrive(&kv_empty[kslot]);
+          B200FA_WAIT(&kv_full[slot], phase, 0x351);
+          mbar_arrive(&kv_empty[slot]);
+          if (++slot == Cfg::kStages) { slot = 0; phase ^= 1; }
+          if (++slot == Cfg::kStages) { slot = 0; phase ^= 1; }
+          if (!take_turn()) goto teardown;
+          mbar_arrive(&turn[1 - t]);
+        }
+      } else if (lane == 0 && n_max > 0) {
+        // this query tile lies wholly past the end of the sequence: release each K/V slot
+        // as it fills and pass every turn straight back
+        int slot = 0;
+        uint32_t phase = 0;
+        for (int k = 0; k <= n_max; ++k) {
+          // block k of the other tile consumes K_0 (k = 0) or V_{k-1} and, if there is one, K_k
+          const int n_release = (k == 0 || k == n_max) ? 1 : 2;
+          for (int r = 0; r < n_release; ++r) {
+            B200FA_WAIT(&kv_full[slot], phase, 0x360);
+            mbar_arrive(&kv_empty[slot]);
+            if (++slot == Cfg::kStages) { slot = 0; phase ^= 1; }
           }
+          if (t == 1) { B200FA_WAIT(&turn[1], k & 1, 0x372); }
+          else if (k > 0) { B200FA_WAIT(&turn[0], (k - 1) & 1, 0x373); }
+          mbar_arrive(&turn[1 - t]);
         }
       }
-    } else if (warp == 13) {
+    } else if (warp == 14) {
       // =========================== TMA producer ===========================
       if (lane == 0 && n_max > 0) {
         int seq = 0;

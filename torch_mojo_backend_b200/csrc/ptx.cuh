@@ -50,6 +50,13 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One arrival on behalf of a whole warp: every lane's earlier shared-memory and TMEM writes
+// are ordered before it (an mbarrier arrival costs a shared-memory atomic, so 32 of them per
+// warp serialise; barriers fed this way are initialised with one count per warp).
+__device__ __forceinline__ void mbar_arrive_warp(uint64_t* bar) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                : "memory");
@@ -206,6 +213,46 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
       ::"r"(d_tmem),
       "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// The issuing thread is a single lane, so every instruction between two MMAs sits on the
+// critical path of the tensor pipe.  These forms take a descriptor as a fixed high word plus
+// a low word (start address field) so that stepping through a tile is one 32-bit add with an
+// immediate, and take the accumulate flag as a compile-time constant.
+struct UmmaDesc {
+  uint32_t lo, hi;
+};
+__device__ __forceinline__ UmmaDesc umma_desc_split(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  const uint64_t d = umma_smem_desc(saddr, lbo_bytes, sbo_bytes);
+  return UmmaDesc{static_cast<uint32_t>(d), static_cast<uint32_t>(d >> 32)};
+}
+// byte offset -> increment of the descriptor's low word
+__host__ __device__ constexpr uint32_t umma_off(uint32_t bytes) { return bytes >> 4; }
+
+template <bool kAcc>
+__device__ __forceinline__ void umma_ss_fast(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                             uint32_t b_hi, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\t"
+      "mov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+      ::"r"(d_tmem),
+      "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "n"(kAcc ? 1 : 0)
+      : "memory");
+}
+template <bool kAcc>
+__device__ __forceinline__ void umma_ts_fast(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
+                                             uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+      ::"r"(d_tmem),
+      "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "n"(kAcc ? 1 : 0)
       : "memory");
 }
 

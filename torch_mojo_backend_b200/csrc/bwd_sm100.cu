@@ -25,6 +25,19 @@
 #include "common.cuh"
 #include "ptx.cuh"
 
+#ifdef B200FA_TRACE
+#define TRACE(role, ev)                                                                          \
+  do {                                                                                           \
+    if (p.status != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 &&          \
+        (threadIdx.x & 31) == 0 && trace_n < 2000) {                                             \
+      reinterpret_cast<unsigned long long*>(p.status + 16)[(role) * 2048 + trace_n++] =          \
+          (static_cast<unsigned long long>(clock64()) << 8) | (ev);                              \
+    }                                                                                            \
+  } while (0)
+#else
+#define TRACE(role, ev) do {} while (0)
+#endif
+
 namespace b200fa {
 namespace {
 
@@ -81,6 +94,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+#ifdef B200FA_TRACE
+  int trace_n = 0;
+#endif
   const int n_tile = blockIdx.x;
   const int hk = blockIdx.y;
   const int b = blockIdx.z;
@@ -154,6 +170,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
       // lse2 rode in with the Q tile; observing its barrier directly makes the bulk copy visible here
       B200FA_WAIT(&q_full[stage], (i / Cfg::kStages) & 1, 0x501);
       tc_fence_after();
+      if ((warp & 3) == 0) TRACE(wg, 1);
       float pf[64];
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
@@ -178,10 +195,12 @@ bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive_warp(p_full);
+      if ((warp & 3) == 0) TRACE(wg, 2);
       // ---- dS^T = P^T * (dP^T - dpsum)
       B200FA_WAIT(dp_full, i & 1, 0x510);
       B200FA_WAIT(&do_full[stage], (i / Cfg::kStages) & 1, 0x511);
       tc_fence_after();
+      if ((warp & 3) == 0) TRACE(wg, 3);
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
         uint32_t d[32];
@@ -208,6 +227,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
       tc_fence_before();
       fence_proxy_async_smem();
       mbar_arrive_warp(ds_full);
+      if ((warp & 3) == 0) TRACE(wg, 4);
     }
     // ---- epilogue: dV and dK (this warpgroup's half of the head dimension)
     B200FA_WAIT(dkdv_full, 0, 0x520);
@@ -261,6 +281,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
                    ((static_cast<int64_t>(b) * p.Hq + h) * p.Spad + m_tile * kTile + row) * kD;
       B200FA_WAIT(dq_full, i & 1, 0x600);
       tc_fence_after();
+      if (warp == 8) TRACE(2, 10);
 #pragma unroll
       for (int ch = 0; ch < kD / 32; ++ch) {
         uint32_t a[32];
@@ -270,6 +291,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
           // every column is in registers: the accumulator columns may be overwritten
           tc_fence_before();
           mbar_arrive_warp(dq_empty);
+          if (warp == 8) TRACE(2, 11);
         }
         const float* af = reinterpret_cast<const float*>(a);
 #pragma unroll
@@ -332,8 +354,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
           const uint32_t nstage_lo = nstage * umma_off(Cfg::kTileBytes);
           const uint32_t nphase = static_cast<uint32_t>(((i + 1) / Cfg::kStages) & 1);
           // dV += P^T dO
+          TRACE(3, 20);
           B200FA_WAIT(p_full, i & 1, 0x710);
           tc_fence_after();
+          TRACE(3, 21);
           issue_ts(tDV, tS, mDO, stage_lo, i > 0);
           // S^T of the next step can start as soon as P^T has been consumed (in issue order)
           if (has_next) {
@@ -343,8 +367,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
             umma_commit(s_full);
           }
           // dK += dS^T Q ; dQ = dS K
+          TRACE(3, 22);
           B200FA_WAIT(ds_full, i & 1, 0x712);
           tc_fence_after();
+          TRACE(3, 23);
           issue_ts(tDK, tDP, mQ, stage_lo, i > 0);
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
@@ -354,10 +380,12 @@ bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
           }
           umma_commit(dq_full);
           umma_commit(&qdo_empty[stage]);
+          TRACE(3, 24);
           if (has_next) {
             B200FA_WAIT(&do_full[nstage], nphase, 0x713);
             B200FA_WAIT(dq_empty, i & 1, 0x714);
             tc_fence_after();
+            TRACE(3, 25);
             issue_kmajor(tDP, kV, kDO, nstage_lo);
             umma_commit(dp_full);
           }

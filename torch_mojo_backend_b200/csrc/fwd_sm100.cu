@@ -49,8 +49,13 @@ constexpr int kSubTileBytes = 128 * 128;  // one 128-row x 64-column (128 B) swi
 // maximum grows by more than this, so P can be as large as 2^8 against a stale maximum.
 constexpr float kRescaleLog2 = 8.f;
 // Of every 8 column pairs, this many take their exponentials on the FMA pipe (range
-// reduction + cubic) instead of the MUFU unit, which would otherwise cap the kernel.
-constexpr int kEmuOf8 = 3;
+// reduction + cubic) instead of the MUFU unit.  Measured on B200 with the two query tiles in
+// anti-phase (one softmax warp per scheduler at a time) the MUFU unit is not saturated and
+// the extra FMA-pipe instructions cost more than they save, so the default is 0.
+#ifndef B200FA_EMU_OF8
+#define B200FA_EMU_OF8 0
+#endif
+constexpr int kEmuOf8 = B200FA_EMU_OF8;
 
 // 2^x for x <= ~127 on the FMA pipe, two values at a time: x = n + f with n = floor(x),
 // 2^f by a cubic fitted on [0,1) (max relative error 8.7e-5, far below 16-bit rounding of

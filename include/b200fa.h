@@ -75,9 +75,10 @@ int b200fa_fwd(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_te
                void* stream, int device, uint32_t* status_word);
 
 /*
- * Scratch bytes b200fa_bwd needs for a problem of this size (fp32 dQ accumulator plus the
- * per-row softmax statistics).  Mirrors the scratch the reference allocates in
- * torch_mojo_backend/eager_kernels/aten_fast.py:7314-7324.
+ * Scratch bytes b200fa_bwd needs for a problem of this size: two fp32 per-row statistic
+ * arrays, (B, Hq, ceil(S/128)*128) each.  The reference allocates the same two arrays plus an
+ * fp32 dQ accumulator (torch_mojo_backend/eager_kernels/aten_fast.py:7314-7324); this library
+ * keeps the dQ accumulator in tensor memory instead.
  */
 size_t b200fa_bwd_workspace_bytes(int64_t batch, int64_t heads_q, int64_t heads_kv, int64_t seqlen,
                                   int64_t head_dim, int dtype);
@@ -103,25 +104,25 @@ int b200fa_bwd(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_te
  * Who needs it: a host that only passes through device pointers owned by some other runtime
  * and has no CUDA allocator to ask for scratch; a backward that runs on a thread where the
  * framework's allocator must not be re-entered; a serving loop that bans allocation once it
- * is warm.  Instead of a workspace argument, the scratch (fp32 dQ accumulator and per-row
- * statistics) lives in a fixed array compiled into the library, B200FA_NO_ALLOC_SCRATCH_BYTES
- * (64 MiB) per GPU, held by every GPU that loads the library until the process exits.
+ * is warm.  Instead of a workspace argument, the scratch (the per-row statistics of the
+ * backward) lives in a fixed array compiled into the library, B200FA_NO_ALLOC_SCRATCH_BYTES
+ * (8 MiB) per GPU, held by every GPU that loads the library until the process exits.
  *
  *   - Problems whose b200fa_bwd_workspace_bytes(...) exceeds that size are refused with
  *     B200FA_ERR_WORKSPACE (b200fa_last_error_detail() says how much was needed); nothing is
- *     launched.  64 MiB covers e.g. B*Hq*S up to 245,760 rows at D=64 or 126,976 rows at
- *     D=128 (GPT-2-small attention, B=8 H=12 S=1024 D=64, needs 26 MB).
+ *     launched.  8 MiB covers B*Hq*ceil(S/128)*128 up to 1,048,576 rows (GPT-2-small
+ *     attention, B=8 H=12 S=1024, needs 0.8 MB; B=4 Hq=32 S=4096 needs 4 MB).
  *   - The call makes no cudaMalloc / cudaFree and calls no allocating routine.  The first
  *     call on each device looks up the array's device address (cudaGetSymbolAddress with that
  *     device current) and caches it; make that first call outside any stream capture.
  *   - All calls on a device share the one array, and it keeps whatever the previous call
- *     left there.  The kernels clear the part that must start at zero (the dQ accumulator)
- *     themselves, on `stream`, before using it.  Because the array is shared, two calls whose
+ *     left there.  Nothing in it has to start at zero: the preprocess kernel overwrites every
+ *     element the other kernels read, on `stream`, before they run.  Because the array is shared, two calls whose
  *     kernels can overlap on the GPU (different streams, or different host threads without
  *     ordering between them) race on it: serialise them on one stream or with events.
  *   - Inputs, outputs, return codes and numerics are those of b200fa_bwd.
  */
-#define B200FA_NO_ALLOC_SCRATCH_BYTES (64u << 20)
+#define B200FA_NO_ALLOC_SCRATCH_BYTES (8u << 20)
 int b200fa_bwd_no_alloc(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_tensor4* v,
                         const b200fa_tensor4* out, const b200fa_tensor4* dout, const float* lse,
                         const b200fa_tensor4* dq, const b200fa_tensor4* dk, const b200fa_tensor4* dv,
@@ -148,8 +149,8 @@ int b200fa_bwd_simt(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200
 
 /*
  * b200fa_bwd restricted to a subset of its three kernels, for timing one kernel alone with
- * CUDA events: `parts` is a bit mask, 1 = preprocess, 2 = the dK/dV/dQ tensor-core kernel,
- * 4 = dQ conversion (7 == b200fa_bwd).  16-bit dtypes only.  Results are only meaningful when
+ * CUDA events: `parts` is a bit mask, 1 = preprocess, 2 = the dK/dV tensor-core kernel,
+ * 4 = the dQ tensor-core kernel (7 == b200fa_bwd).  16-bit dtypes only.  Results are only meaningful when
  * the parts are run in order; it has no counterpart in the reference.
  */
 int b200fa_bwd_parts(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_tensor4* v,

@@ -43,12 +43,12 @@ def test_strerror_covers_all_codes():
 
 
 def test_workspace_formula():
-    # 2 x (B*Hq*Spad) fp32 statistics + (B*Hq*Spad*D) fp32 dQ accumulator, Spad = ceil(S/128)*128
-    # (the reference's scratch: aten_fast.py:7314-7324)
+    # 2 x (B*Hq*Spad) fp32 row statistics, Spad = ceil(S/128)*128 (the reference's scratch,
+    # aten_fast.py:7314-7324, minus its fp32 dQ accumulator: dQ accumulates in tensor memory)
     B, Hq, Hkv, S, D = 8, 12, 12, 1024, 64
     rows = B * Hq * 1024
-    assert _lib.bwd_workspace_bytes(B, Hq, Hkv, S, D, _lib.BF16) == 2 * rows * 4 + rows * D * 4
-    assert _lib.bwd_workspace_bytes(1, 1, 1, 65, 64, _lib.BF16) == 2 * 512 + 128 * 64 * 4
+    assert _lib.bwd_workspace_bytes(B, Hq, Hkv, S, D, _lib.BF16) == 2 * rows * 4
+    assert _lib.bwd_workspace_bytes(1, 1, 1, 65, 64, _lib.BF16) == 2 * 512
     assert _lib.bwd_workspace_bytes(0, 1, 1, 65, 64, _lib.BF16) == 0
 
 

@@ -164,8 +164,7 @@ def test_full_size_properties_config3():
     # backward: linear in dO; dV with P fixed; deterministic dK/dV
     dq, dk, dv = raw.flash_bwd(dout, q, k, v, out, lse, causal=True, scale=cfg.scale)
     dq2, dk2, dv2 = raw.flash_bwd(dout, q, k, v, out, lse, causal=True, scale=cfg.scale)
-    assert torch.equal(dk, dk2) and torch.equal(dv, dv2)
-    assert (dq.float() - dq2.float()).abs().max().item() < 2e-2  # fp32 atomics: order may differ
+    assert torch.equal(dk, dk2) and torch.equal(dv, dv2) and torch.equal(dq, dq2)  # no atomics anywhere
     # softmax gradient rows sum to zero: sum_k dS = 0  =>  dq . 1-direction check via dpsum identity
     half = (dout.float() * 0.5).to(dout.dtype)
     _, _, dv_half = raw.flash_bwd(half, q, k, v, out, lse, causal=True, scale=cfg.scale)

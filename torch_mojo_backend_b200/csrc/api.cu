@@ -212,7 +212,8 @@ size_t b200fa_bwd_workspace_bytes(int64_t batch, int64_t heads_q, int64_t heads_
   if (batch <= 0 || heads_q <= 0 || seqlen <= 0 || head_dim <= 0) return 0;
   const size_t spad = static_cast<size_t>((seqlen + 127) / 128 * 128);
   const size_t rows = static_cast<size_t>(batch) * heads_q * spad;
-  return 2 * align256(rows * 4) + align256(rows * head_dim * 4);
+  // two fp32 row-statistic arrays (rowsum(dO*O) and lse*log2e), padded to whole 128-row tiles
+  return 2 * align256(rows * 4);
 }
 
 static int bwd_impl(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_tensor4* v,
@@ -249,7 +250,7 @@ static int bwd_impl(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   p.dpsum = reinterpret_cast<float*>(ws);
   p.lse_log2 = reinterpret_cast<float*>(ws + align256(rows * 4));
-  p.dq_accum = reinterpret_cast<float*>(ws + 2 * align256(rows * 4));
+  p.dq_accum = nullptr;  // no global dQ accumulation: the dQ kernel keeps its accumulator in TMEM
   p.lse = lse;
   p.B = static_cast<int>(B); p.Hq = static_cast<int>(Hq); p.Hkv = static_cast<int>(Hkv);
   p.S = static_cast<int>(S); p.Spad = static_cast<int>(spad); p.D = static_cast<int>(D);

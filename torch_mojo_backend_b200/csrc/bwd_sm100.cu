@@ -1,27 +1,26 @@
-// Backward flash attention for sm_100a: preprocess, a dK/dV/dQ tcgen05 pipeline, and the
-// fp32 -> 16-bit dQ conversion.
+// Backward flash attention for sm_100a: a preprocess pass and two tcgen05 kernels, one that
+// owns dK/dV and one that owns dQ.
 //
-// Math (same as the reference's three backward kernels,
+// Math (same as the reference's backward kernels,
 // torch_mojo_backend/eager_flash_attention/fa4_bwd_kernel.mojo:1-44, 810-980, 1443-1444,
 // 1634-1662, 1855), with c = scale*log2(e):
-//   dpsum = rowsum(dO * O)                      (preprocess; also lse2 = lse*log2(e))
-//   S^T   = K Q^T          dP^T = V dO^T        (tensor core, transposed so that ...)
-//   P^T   = exp2(S^T*c - lse2)                  (... P^T / dS^T land in TMEM as A operands)
-//   dV   += P^T dO         dS^T = P^T * (dP^T - dpsum)
-//   dK   += dS^T Q         dQ  += dS K          (dQ accumulated in fp32 global memory)
-//   dK *= scale (epilogue), dQ *= scale (convert kernel)
+//   dpsum = rowsum(dO * O),  lse2 = lse*log2(e)              (preprocess)
+//   P  = exp2(S*c - lse2),   dS = P * (dP - dpsum)
+//   dV = P^T dO,   dK = scale * dS^T Q,   dQ = scale * dS K
 //
-// One CTA owns one 128-row K/V tile of one (batch, kv head) and walks every query tile at
-// or below the causal diagonal, for every query head of the GQA group, so dK and dV
-// accumulate in tensor memory without atomics.
+// The reference accumulates dQ from every K/V tile into an fp32 buffer with bulk reduce-adds
+// and converts it afterwards.  On B200 that accumulation is the bottleneck: fp32 reductions
+// into L2 sustain 1.9-3.3 TB/s depending on the access pattern, and a 4k-token Llama-style
+// backward needs 4.4 GB of them.  Here nothing is accumulated in global memory: the
+// dK/dV kernel gives each CTA one 128-row K/V tile (S^T = K Q^T, dP^T = V dO^T, so P^T and
+// dS^T land in tensor memory as the A operands of dV += P^T dO and dK += dS^T Q), and the dQ
+// kernel gives each CTA one 128-row query tile (S = Q K^T, dP = dO V^T, dS in tensor memory
+// as the A operand of dQ += dS K).  S and dP are computed twice (7 tile GEMMs per tile pair
+// instead of 5), every accumulator lives in TMEM, and the results are deterministic.
 //
-//   warps 0-3   compute, query columns 0-63 of each S^T / dP^T tile  (thread <-> key row)
-//   warps 4-7   compute, query columns 64-127
-//   warps 8-11  dQ drain: TMEM -> red.global.add.f32 into the fp32 accumulator
-//   warp  12    MMA issuer          warp 13   TMA producer        warps 14-15 idle
-//
-// TMEM columns: [0,128) S^T, overwritten in place by 16-bit P^T; [128,256) dP^T, overwritten
-// by 16-bit dS^T and then by the dQ accumulator; dV and dK after that.
+// Both kernels: warps 0-3 and 4-7 are two compute warpgroups that split the 128 score
+// columns of a tile in halves (thread <-> TMEM lane), warp 8 issues the MMAs, warp 9 drives
+// TMA, warps 10-11 idle.
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -42,7 +41,7 @@ namespace b200fa {
 namespace {
 
 constexpr int kTile = 128;
-constexpr int kThreads = 512;
+constexpr int kThreads = 384;
 constexpr int kSubTileBytes = 128 * 128;
 
 template <int kD>
@@ -50,46 +49,60 @@ struct BwdCfg {
   static constexpr int kTileBytes = kTile * kD * 2;
   static constexpr int kSub = kD / 64;
   static constexpr int kStages = 2;
-  static constexpr int kTmemS = 0, kTmemDP = 128, kTmemDV = 256, kTmemDK = 256 + kD;
-  // D=128 has no spare columns, so dQ re-uses the dP columns; D=64 gives it its own
-  static constexpr int kTmemDQ = (kD == 128) ? kTmemDP : (256 + 2 * kD);
-  static constexpr int kOffK = 0;
-  static constexpr int kOffV = kTileBytes;
-  static constexpr int kOffQ = 2 * kTileBytes;
-  static constexpr int kOffDO = kOffQ + kStages * kTileBytes;
-  static constexpr int kOffDS = kOffDO + kStages * kTileBytes;
-  static constexpr int kOffStat = kOffDS + 128 * 128 * 2;         // [stage][lse2|dpsum][128] fp32
+  // resident pair of tiles, then kStages pairs of streamed tiles, then per-stage row statistics
+  static constexpr int kOffResident = 0;
+  static constexpr int kOffStream = 2 * kTileBytes;
+  static constexpr int kOffStat = kOffStream + kStages * 2 * kTileBytes;  // [stage][lse2|dpsum][128] fp32
   static constexpr int kOffBars = kOffStat + kStages * 2 * 128 * 4;
-  static constexpr int kNumBars = 1 + 3 * kStages + 7;
+  static constexpr int kNumBars = 16;
   static constexpr int kSmemBytes = kOffBars + kNumBars * 8 + 16;
 };
 
+template <bool kBf16>
+__device__ __forceinline__ void store_row_16bit(uint16_t* dst, const float* v, float mul) {
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    uint4 w;
+    w.x = pack2<kBf16>(v[g * 8 + 0] * mul, v[g * 8 + 1] * mul);
+    w.y = pack2<kBf16>(v[g * 8 + 2] * mul, v[g * 8 + 3] * mul);
+    w.z = pack2<kBf16>(v[g * 8 + 4] * mul, v[g * 8 + 5] * mul);
+    w.w = pack2<kBf16>(v[g * 8 + 6] * mul, v[g * 8 + 7] * mul);
+    *reinterpret_cast<uint4*>(dst + g * 8) = w;
+  }
+}
+
+#define B200FA_WAIT(bar, parity, site) \
+  if (!mbar_wait((bar), (parity), abort_flag, p.status, (site))) goto teardown
+
+// ------------------------------------------------------------------------------------------
+// dK / dV kernel.  One CTA = one 128-row K/V tile of one (batch, kv head); it walks every
+// query tile at or below the causal diagonal for every query head of the GQA group.
+// TMEM columns: [0,128) S^T, overwritten in place by 16-bit P^T; [128,256) dP^T, overwritten
+// by 16-bit dS^T; then dV and dK accumulators.
+// ------------------------------------------------------------------------------------------
 template <int kD, bool kBf16, bool kCausal>
 __global__ void __launch_bounds__(kThreads, 1)
-bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
-           const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
-           const BwdParams p) {
+bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+                const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
+                const BwdParams p) {
   using Cfg = BwdCfg<kD>;
+  constexpr int kTmemS = 0, kTmemDP = 128, kTmemDV = 256, kTmemDK = 256 + kD;
   extern __shared__ __align__(1024) uint8_t smem[];
-  uint8_t* sK = smem + Cfg::kOffK;
-  uint8_t* sV = smem + Cfg::kOffV;
-  uint8_t* sQ = smem + Cfg::kOffQ;
-  uint8_t* sDO = smem + Cfg::kOffDO;
-  uint8_t* sDS = smem + Cfg::kOffDS;
+  uint8_t* sK = smem + Cfg::kOffResident;
+  uint8_t* sV = sK + Cfg::kTileBytes;
+  uint8_t* sQ = smem + Cfg::kOffStream;                          // stage s: sQ + s * 2 * tile, dO right behind
   float* sStat = reinterpret_cast<float*>(smem + Cfg::kOffStat);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBars);
-  uint64_t* kv_full = bars;                       // [1]
-  uint64_t* q_full = kv_full + 1;                 // [kStages]  Q tile + lse2
-  uint64_t* do_full = q_full + Cfg::kStages;      // [kStages]  dO tile + dpsum
-  uint64_t* qdo_empty = do_full + Cfg::kStages;   // [kStages]
-  uint64_t* s_full = qdo_empty + Cfg::kStages;    // S^T ready
-  uint64_t* dp_full = s_full + 1;                 // dP^T ready
-  uint64_t* p_full = dp_full + 1;                 // P^T written (8 warp arrivals)
-  uint64_t* ds_full = p_full + 1;                 // dS^T written (8 warp arrivals)
-  uint64_t* dq_full = ds_full + 1;                // dQ tile ready
-  uint64_t* dq_empty = dq_full + 1;               // dQ tile drained (4 warp arrivals)
-  uint64_t* dkdv_full = dq_empty + 1;             // everything accumulated
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dkdv_full + 1);
+  uint64_t* kv_full = bars;                        // [1]
+  uint64_t* q_full = kv_full + 1;                  // [kStages]  Q tile + lse2
+  uint64_t* do_full = q_full + Cfg::kStages;       // [kStages]  dO tile + dpsum
+  uint64_t* qdo_empty = do_full + Cfg::kStages;    // [kStages]
+  uint64_t* s_full = qdo_empty + Cfg::kStages;     // S^T ready
+  uint64_t* dp_full = s_full + 1;                  // dP^T ready
+  uint64_t* p_full = dp_full + 1;                  // P^T written  (8 warp arrivals)
+  uint64_t* ds_full = p_full + 1;                  // dS^T written (8 warp arrivals)
+  uint64_t* acc_full = ds_full + 1;                // dK, dV complete
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::kNumBars);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -112,7 +125,6 @@ bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
     if (threadIdx.x == 0 && p.status) atomicCAS(p.status, kStatusOk, 0x414c0000u);
     return;
   }
-
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
     for (int i = 0; i < Cfg::kStages; ++i) {
@@ -122,21 +134,18 @@ bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
     }
     mbar_init(s_full, 1);
     mbar_init(dp_full, 1);
-    // one elected arrival per warp: 8 compute warps, 4 drain warps
-    mbar_init(p_full, 8);
+    mbar_init(p_full, 8);   // one elected arrival per compute warp
     mbar_init(ds_full, 8);
-    mbar_init(dq_full, 1);
-    mbar_init(dq_empty, 4);
-    mbar_init(dkdv_full, 1);
+    mbar_init(acc_full, 1);
     *abort_flag = 0;
     fence_mbar_init();
     fence_proxy_async_smem();
   }
-  if (warp == 12) {
+  if (warp == 8) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
-  if (warp == 13 && lane == 0) {
+  if (warp == 9 && lane == 0) {
     tma_prefetch_desc(&mapQ);
     tma_prefetch_desc(&mapK);
     tma_prefetch_desc(&mapV);
@@ -147,28 +156,24 @@ bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-#define B200FA_WAIT(bar, parity, site) \
-  if (!mbar_wait((bar), (parity), abort_flag, p.status, (site))) goto teardown
-
   if (warp < 8) {
     // =========================== compute warps ===========================
-    reg_alloc<168>();
-    const int wg = warp >> 2;                       // which 64-column half of the query tile
+    const int wg = warp >> 2;                       // which 64-column (query) half of the tile
     const int j = (warp & 3) * 32 + lane;           // key row inside the tile == TMEM lane
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t tS = tmem_base + lane_off + Cfg::kTmemS + wg * 64;
-    const uint32_t tDP = tmem_base + lane_off + Cfg::kTmemDP + wg * 64;
+    const uint32_t tS = tmem_base + lane_off + kTmemS + wg * 64;
+    const uint32_t tDP = tmem_base + lane_off + kTmemDP + wg * 64;
     const float c = p.scale_log2;
-    uint8_t* ds_row = sDS + wg * kSubTileBytes + j * 128;
     for (int i = 0; i < steps; ++i) {
       const int stage = i % Cfg::kStages;
+      const uint32_t ring_phase = static_cast<uint32_t>((i / Cfg::kStages) & 1);
       const int m_tile = m_start + i % per_head;
-      const float* lse2 = sStat + stage * 256 + wg * 64;
-      const float* dps = lse2 + 128;
+      const float4* lse2 = reinterpret_cast<const float4*>(sStat + stage * 256 + wg * 64);
+      const float4* dps = lse2 + 32;
       // ---- P^T = exp2(S^T * c - lse2)
       B200FA_WAIT(s_full, i & 1, 0x500);
       // lse2 rode in with the Q tile; observing its barrier directly makes the bulk copy visible here
-      B200FA_WAIT(&q_full[stage], (i / Cfg::kStages) & 1, 0x501);
+      B200FA_WAIT(&q_full[stage], ring_phase, 0x501);
       tc_fence_after();
       if ((warp & 3) == 0) TRACE(wg, 1);
       float pf[64];
@@ -178,16 +183,22 @@ bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
         tmem_ld32(tS + ch * 32, s);
         tmem_wait_ld();
         const float* sf = reinterpret_cast<const float*>(s);
-        uint32_t pk[16];
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          float v = ex2_approx(fmaf(sf[e], c, -lse2[ch * 32 + e]));
-          if (kCausal && m_tile == n_tile) {
-            // on the diagonal tile, query column q sees key row j only if j <= q
-            if (j > wg * 64 + ch * 32 + e) v = 0.f;
-          }
-          pf[ch * 32 + e] = v;
+        for (int e4 = 0; e4 < 8; ++e4) {
+          const float4 l4 = lse2[ch * 8 + e4];
+          pf[ch * 32 + e4 * 4 + 0] = ex2_approx(fmaf(sf[e4 * 4 + 0], c, -l4.x));
+          pf[ch * 32 + e4 * 4 + 1] = ex2_approx(fmaf(sf[e4 * 4 + 1], c, -l4.y));
+          pf[ch * 32 + e4 * 4 + 2] = ex2_approx(fmaf(sf[e4 * 4 + 2], c, -l4.z));
+          pf[ch * 32 + e4 * 4 + 3] = ex2_approx(fmaf(sf[e4 * 4 + 3], c, -l4.w));
         }
+        if (kCausal && m_tile == n_tile) {
+          // on the diagonal tile, query column q sees key row j only if j <= q
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            if (j > wg * 64 + ch * 32 + e) pf[ch * 32 + e] = 0.f;
+          }
+        }
+        uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) pk[e] = pack2<kBf16>(pf[ch * 32 + 2 * e], pf[ch * 32 + 2 * e + 1]);
         tmem_st16(tS + ch * 16, pk);
@@ -198,7 +209,282 @@ bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
       if ((warp & 3) == 0) TRACE(wg, 2);
       // ---- dS^T = P^T * (dP^T - dpsum)
       B200FA_WAIT(dp_full, i & 1, 0x510);
-      B200FA_WAIT(&do_full[stage], (i / Cfg::kStages) & 1, 0x511);
+      B200FA_WAIT(&do_full[stage], ring_phase, 0x511);
+      tc_fence_after();
+      if ((warp & 3) == 0) TRACE(wg, 3);
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {
+        uint32_t d[32];
+        tmem_ld32(tDP + ch * 32, d);
+        tmem_wait_ld();
+        const float* df = reinterpret_cast<const float*>(d);
+        uint32_t pk[16];
+#pragma unroll
+        for (int e4 = 0; e4 < 8; ++e4) {
+          const float4 d4 = dps[ch * 8 + e4];
+          const float a0 = pf[ch * 32 + e4 * 4 + 0] * (df[e4 * 4 + 0] - d4.x);
+          const float a1 = pf[ch * 32 + e4 * 4 + 1] * (df[e4 * 4 + 1] - d4.y);
+          const float a2 = pf[ch * 32 + e4 * 4 + 2] * (df[e4 * 4 + 2] - d4.z);
+          const float a3 = pf[ch * 32 + e4 * 4 + 3] * (df[e4 * 4 + 3] - d4.w);
+          pk[e4 * 2] = pack2<kBf16>(a0, a1);
+          pk[e4 * 2 + 1] = pack2<kBf16>(a2, a3);
+        }
+        tmem_st16(tDP + ch * 16, pk);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive_warp(ds_full);
+      if ((warp & 3) == 0) TRACE(wg, 4);
+    }
+    // ---- epilogue: dV and dK (this warpgroup's half of the head dimension)
+    B200FA_WAIT(acc_full, 0, 0x520);
+    tc_fence_after();
+    {
+      const int krow = n0 + j;
+      const bool valid = krow < p.S;
+      constexpr int kHalf = kD / 2;
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        const View4& dst_view = which == 0 ? p.dv : p.dk;
+        uint16_t* dst = reinterpret_cast<uint16_t*>(dst_view.ptr) +
+                        (static_cast<int64_t>(b) * dst_view.sb + static_cast<int64_t>(hk) * dst_view.sh +
+                         static_cast<int64_t>(krow) * dst_view.ss) + wg * kHalf;
+        const uint32_t tacc = tmem_base + lane_off + (which == 0 ? kTmemDV : kTmemDK) + wg * kHalf;
+        const float mul = which == 0 ? 1.f : p.scale;
+#pragma unroll
+        for (int ch = 0; ch < kHalf / 32; ++ch) {
+          uint32_t a[32];
+          tmem_ld32(tacc + ch * 32, a);
+          tmem_wait_ld();
+          if (valid) store_row_16bit<kBf16>(dst + ch * 32, reinterpret_cast<const float*>(a), mul);
+        }
+      }
+    }
+  } else if (warp == 8) {
+    // =========================== MMA issuer ===========================
+    if (lane == 0) {
+      constexpr uint32_t idesc_st = umma_idesc(kBf16, false, false, 128, 128);  // S^T, dP^T
+      constexpr uint32_t idesc_acc = umma_idesc(kBf16, false, true, 128, kD);   // dV, dK (A from TMEM)
+      const uint32_t tS = tmem_base + kTmemS, tDP = tmem_base + kTmemDP, tDV = tmem_base + kTmemDV,
+                     tDK = tmem_base + kTmemDK;
+      // Descriptors: fixed high word + start-address low word.  K-major form for the S^T / dP^T
+      // operands, MN-major form (LBO = next 64-column sub-tile) when Q / dO are the B operand
+      // of an accumulating MMA.
+      const UmmaDesc kK = umma_desc_split(smem_u32(sK), 16, 1024), kV = umma_desc_split(smem_u32(sV), 16, 1024),
+                     kQ = umma_desc_split(smem_u32(sQ), 16, 1024),
+                     kDO = umma_desc_split(smem_u32(sQ) + Cfg::kTileBytes, 16, 1024);
+      const UmmaDesc mQ = umma_desc_split(smem_u32(sQ), kSubTileBytes, 1024),
+                     mDO = umma_desc_split(smem_u32(sQ) + Cfg::kTileBytes, kSubTileBytes, 1024);
+      // D[128 x 128] = A[128 x kD] * B[128 x kD]^T, both K-major
+      auto issue_kmajor = [&](uint32_t d_tmem, const UmmaDesc& a, const UmmaDesc& bd, uint32_t b_stage_lo) {
+#pragma unroll
+        for (int kk = 0; kk < kD / 16; ++kk) {
+          const uint32_t off = umma_off((kk >> 2) * kSubTileBytes + (kk & 3) * 32);
+          if (kk == 0) umma_ss_fast<false>(d_tmem, a.lo + off, a.hi, bd.lo + b_stage_lo + off, bd.hi, idesc_st);
+          else         umma_ss_fast<true>(d_tmem, a.lo + off, a.hi, bd.lo + b_stage_lo + off, bd.hi, idesc_st);
+        }
+      };
+      // D[128 x kD] (+)= A-in-TMEM[128 x 128] * B[128 x kD] (B rows are the contraction index)
+      auto issue_ts = [&](uint32_t d_tmem, uint32_t a_tmem, const UmmaDesc& bd, uint32_t b_stage_lo, bool first) {
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t a_col = (kk < 4) ? kk * 8 : 64 + (kk - 4) * 8;
+          const uint32_t b_lo = bd.lo + b_stage_lo + umma_off(kk * 2048);
+          if (kk == 0 && first) umma_ts_fast<false>(d_tmem, a_tmem + a_col, b_lo, bd.hi, idesc_acc);
+          else                  umma_ts_fast<true>(d_tmem, a_tmem + a_col, b_lo, bd.hi, idesc_acc);
+        }
+      };
+      constexpr uint32_t kStageLo = umma_off(2 * Cfg::kTileBytes);
+      B200FA_WAIT(kv_full, 0, 0x700);
+      B200FA_WAIT(&q_full[0], 0, 0x701);
+      tc_fence_after();
+      issue_kmajor(tS, kK, kQ, 0);
+      umma_commit(s_full);
+      B200FA_WAIT(&do_full[0], 0, 0x702);
+      tc_fence_after();
+      issue_kmajor(tDP, kV, kDO, 0);
+      umma_commit(dp_full);
+      for (int i = 0; i < steps; ++i) {
+        const int stage = i % Cfg::kStages;
+        const uint32_t stage_lo = stage * kStageLo;
+        const bool has_next = (i + 1 < steps);
+        const int nstage = (i + 1) % Cfg::kStages;
+        const uint32_t nphase = static_cast<uint32_t>(((i + 1) / Cfg::kStages) & 1);
+        const uint32_t nstage_lo = nstage * kStageLo;
+        if (has_next) { B200FA_WAIT(&q_full[nstage], nphase, 0x711); }
+        // dV += P^T dO, then S^T of the next step (it overwrites P^T, in issue order)
+        B200FA_WAIT(p_full, i & 1, 0x710);
+        tc_fence_after();
+        TRACE(3, 21);
+        issue_ts(tDV, tS, mDO, stage_lo, i == 0);
+        if (has_next) {
+          issue_kmajor(tS, kK, kQ, nstage_lo);
+          umma_commit(s_full);
+        }
+        if (has_next) { B200FA_WAIT(&do_full[nstage], nphase, 0x713); }
+        // dK += dS^T Q, then dP^T of the next step (it overwrites dS^T, in issue order)
+        B200FA_WAIT(ds_full, i & 1, 0x712);
+        tc_fence_after();
+        TRACE(3, 23);
+        issue_ts(tDK, tDP, mQ, stage_lo, i == 0);
+        umma_commit(&qdo_empty[stage]);
+        if (has_next) {
+          issue_kmajor(tDP, kV, kDO, nstage_lo);
+          umma_commit(dp_full);
+        }
+      }
+      umma_commit(acc_full);
+    }
+  } else if (warp == 9) {
+    // =========================== TMA producer ===========================
+    if (lane == 0) {
+      auto load_tile = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int srow, int head) {
+#pragma unroll
+        for (int cs = 0; cs < Cfg::kSub; ++cs) tma_load_4d(dst + cs * kSubTileBytes, map, bar, cs * 64, srow, head, b);
+      };
+      mbar_arrive_expect_tx(kv_full, 2 * Cfg::kTileBytes);
+      load_tile(&mapK, sK, kv_full, n0, hk);
+      load_tile(&mapV, sV, kv_full, n0, hk);
+      for (int i = 0; i < steps; ++i) {
+        const int stage = i % Cfg::kStages;
+        const int g = i / per_head;
+        const int m_tile = m_start + i % per_head;
+        const int h = hk * group + g;
+        if (i >= Cfg::kStages) {
+          B200FA_WAIT(&qdo_empty[stage], ((i / Cfg::kStages) - 1) & 1, 0x800);
+        }
+        const int64_t stat_off = (static_cast<int64_t>(b) * p.Hq + h) * p.Spad + m_tile * kTile;
+        float* st = sStat + stage * 256;
+        uint8_t* q_dst = sQ + stage * 2 * Cfg::kTileBytes;
+        mbar_arrive_expect_tx(&q_full[stage], Cfg::kTileBytes + 512);
+        load_tile(&mapQ, q_dst, &q_full[stage], m_tile * kTile, h);
+        bulk_load_1d(st, p.lse_log2 + stat_off, 512, &q_full[stage]);
+        mbar_arrive_expect_tx(&do_full[stage], Cfg::kTileBytes + 512);
+        load_tile(&mapDO, q_dst + Cfg::kTileBytes, &do_full[stage], m_tile * kTile, h);
+        bulk_load_1d(st + 128, p.dpsum + stat_off, 512, &do_full[stage]);
+      }
+    }
+  }
+
+teardown:
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// dQ kernel.  One CTA = one 128-row query tile of one (batch, query head); it walks the K/V
+// tiles up to the causal diagonal.  Thread <-> query row, so lse2 and dpsum are per-thread
+// scalars.  TMEM columns: S double-buffered at [0,128) and [128,256) (16-bit dS overwrites
+// the buffer it was computed from), dP at [256,384), the dQ accumulator after that.
+// ------------------------------------------------------------------------------------------
+template <int kD, bool kBf16, bool kCausal>
+__global__ void __launch_bounds__(kThreads, 1)
+bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+              const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
+              const BwdParams p) {
+  using Cfg = BwdCfg<kD>;
+  constexpr int kTmemS = 0, kTmemDP = 256, kTmemDQ = 384;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* sQ = smem + Cfg::kOffResident;
+  uint8_t* sDO = sQ + Cfg::kTileBytes;
+  uint8_t* sKV = smem + Cfg::kOffStream;          // stage s: K at sKV + s * 2 * tile, V right behind
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBars);
+  uint64_t* qdo_full = bars;                       // [1]
+  uint64_t* kv_full = qdo_full + 1;                // [kStages]
+  uint64_t* kv_empty = kv_full + Cfg::kStages;     // [kStages]
+  uint64_t* s_full = kv_empty + Cfg::kStages;      // [2]  S buffer ready
+  uint64_t* dp_full = s_full + 2;                  // dP ready
+  uint64_t* ds_full = dp_full + 1;                 // dS written, dP consumed (8 warp arrivals)
+  uint64_t* acc_full = ds_full + 1;                // dQ complete
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::kNumBars);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+#ifdef B200FA_TRACE
+  int trace_n = 0;
+#endif
+  const int m_tiles = (p.S + kTile - 1) / kTile;
+  const int m_tile = m_tiles - 1 - static_cast<int>(blockIdx.x);  // heaviest (latest) causal tiles first
+  const int h = blockIdx.y;
+  const int b = blockIdx.z;
+  const int hk = h / (p.Hq / p.Hkv);
+  const int m0 = m_tile * kTile;
+  const int n_tiles = kCausal ? (m_tile + 1) : m_tiles;
+
+  if ((smem_u32(smem) & 1023u) != 0u) {
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, kStatusOk, 0x414c0001u);
+    return;
+  }
+  if (threadIdx.x == 0) {
+    mbar_init(qdo_full, 1);
+    for (int i = 0; i < Cfg::kStages; ++i) {
+      mbar_init(&kv_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+    }
+    mbar_init(&s_full[0], 1);
+    mbar_init(&s_full[1], 1);
+    mbar_init(dp_full, 1);
+    mbar_init(ds_full, 8);
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 8) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  if (warp == 9 && lane == 0) {
+    tma_prefetch_desc(&mapQ);
+    tma_prefetch_desc(&mapK);
+    tma_prefetch_desc(&mapV);
+    tma_prefetch_desc(&mapDO);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp < 8) {
+    // =========================== compute warps ===========================
+    const int wg = warp >> 2;                      // which 64-column (key) half of the tile
+    const int r = (warp & 3) * 32 + lane;          // query row inside the tile == TMEM lane
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tDP = tmem_base + lane_off + kTmemDP + wg * 64;
+    const float c = p.scale_log2;
+    const int64_t stat = (static_cast<int64_t>(b) * p.Hq + h) * p.Spad + m0 + r;  // padded rows exist
+    const float lse2 = p.lse_log2[stat];
+    const float dps = p.dpsum[stat];
+    for (int j = 0; j < n_tiles; ++j) {
+      const int buf = j & 1;
+      const uint32_t tS = tmem_base + lane_off + kTmemS + buf * 128 + wg * 64;
+      B200FA_WAIT(&s_full[buf], (j >> 1) & 1, 0x900);
+      tc_fence_after();
+      if ((warp & 3) == 0) TRACE(wg, 1);
+      float pf[64];
+#pragma unroll
+      for (int ch = 0; ch < 2; ++ch) {
+        uint32_t s[32];
+        tmem_ld32(tS + ch * 32, s);
+        tmem_wait_ld();
+        const float* sf = reinterpret_cast<const float*>(s);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) pf[ch * 32 + e] = ex2_approx(fmaf(sf[e], c, -lse2));
+        if (kCausal && j == m_tile) {
+          // diagonal tile: query row r sees key column only if column <= r
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            if (wg * 64 + ch * 32 + e > r) pf[ch * 32 + e] = 0.f;
+          }
+        }
+      }
+      B200FA_WAIT(dp_full, j & 1, 0x910);
       tc_fence_after();
       if ((warp & 3) == 0) TRACE(wg, 3);
 #pragma unroll
@@ -210,234 +496,139 @@ bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-          const float a0 = pf[ch * 32 + 2 * e] * (df[2 * e] - dps[ch * 32 + 2 * e]);
-          const float a1 = pf[ch * 32 + 2 * e + 1] * (df[2 * e + 1] - dps[ch * 32 + 2 * e + 1]);
+          const float a0 = pf[ch * 32 + 2 * e] * (df[2 * e] - dps);
+          const float a1 = pf[ch * 32 + 2 * e + 1] * (df[2 * e + 1] - dps);
           pk[e] = pack2<kBf16>(a0, a1);
         }
-        tmem_st16(tDP + ch * 16, pk);
-        // the same values, as the 128-byte-swizzled [key row][query column] tile the dQ MMA reads
-#pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          const int chunk = ch * 4 + v;
-          *reinterpret_cast<uint4*>(ds_row + ((chunk ^ (j & 7)) << 4)) =
-              make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]);
-        }
+        tmem_st16(tS + ch * 16, pk);
       }
       tmem_wait_st();
       tc_fence_before();
-      fence_proxy_async_smem();
       mbar_arrive_warp(ds_full);
       if ((warp & 3) == 0) TRACE(wg, 4);
     }
-    // ---- epilogue: dV and dK (this warpgroup's half of the head dimension)
-    B200FA_WAIT(dkdv_full, 0, 0x520);
+    // ---- epilogue: dQ (this warpgroup's half of the head dimension)
+    B200FA_WAIT(acc_full, 0, 0x920);
     tc_fence_after();
     {
-      const int krow = n0 + j;
-      const bool valid = krow < p.S;
+      const int qrow = m0 + r;
+      const bool valid = qrow < p.S;
       constexpr int kHalf = kD / 2;
-      uint16_t* dv_row = reinterpret_cast<uint16_t*>(p.dv.ptr) +
-                         (static_cast<int64_t>(b) * p.dv.sb + static_cast<int64_t>(hk) * p.dv.sh +
-                          static_cast<int64_t>(krow) * p.dv.ss) + wg * kHalf;
-      uint16_t* dk_row = reinterpret_cast<uint16_t*>(p.dk.ptr) +
-                         (static_cast<int64_t>(b) * p.dk.sb + static_cast<int64_t>(hk) * p.dk.sh +
-                          static_cast<int64_t>(krow) * p.dk.ss) + wg * kHalf;
+      uint16_t* dst = reinterpret_cast<uint16_t*>(p.dq.ptr) +
+                      (static_cast<int64_t>(b) * p.dq.sb + static_cast<int64_t>(h) * p.dq.sh +
+                       static_cast<int64_t>(qrow) * p.dq.ss) + wg * kHalf;
+      const uint32_t tacc = tmem_base + lane_off + kTmemDQ + wg * kHalf;
 #pragma unroll
-      for (int which = 0; which < 2; ++which) {
-        const uint32_t tacc = tmem_base + lane_off + (which == 0 ? Cfg::kTmemDV : Cfg::kTmemDK) + wg * kHalf;
-        uint16_t* dst = which == 0 ? dv_row : dk_row;
-        const float mul = which == 0 ? 1.f : p.scale;
-#pragma unroll
-        for (int ch = 0; ch < kHalf / 32; ++ch) {
-          uint32_t a[32];
-          tmem_ld32(tacc + ch * 32, a);
-          tmem_wait_ld();
-          if (valid) {
-            const float* af = reinterpret_cast<const float*>(a);
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              uint4 w;
-              w.x = pack2<kBf16>(af[v * 8 + 0] * mul, af[v * 8 + 1] * mul);
-              w.y = pack2<kBf16>(af[v * 8 + 2] * mul, af[v * 8 + 3] * mul);
-              w.z = pack2<kBf16>(af[v * 8 + 4] * mul, af[v * 8 + 5] * mul);
-              w.w = pack2<kBf16>(af[v * 8 + 6] * mul, af[v * 8 + 7] * mul);
-              *reinterpret_cast<uint4*>(dst + ch * 32 + v * 8) = w;
-            }
-          }
-        }
-      }
-    }
-  } else if (warp < 12) {
-    // =========================== dQ drain warps ===========================
-    reg_dealloc<88>();
-    const int row = (warp & 3) * 32 + lane;  // query row inside the tile == TMEM lane
-    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t tDQ = tmem_base + lane_off + Cfg::kTmemDQ;
-    for (int i = 0; i < steps; ++i) {
-      const int g = i / per_head;
-      const int m_tile = m_start + i % per_head;
-      const int h = hk * group + g;
-      float* acc = p.dq_accum +
-                   ((static_cast<int64_t>(b) * p.Hq + h) * p.Spad + m_tile * kTile + row) * kD;
-      B200FA_WAIT(dq_full, i & 1, 0x600);
-      tc_fence_after();
-      if (warp == 8) TRACE(2, 10);
-#pragma unroll
-      for (int ch = 0; ch < kD / 32; ++ch) {
+      for (int ch = 0; ch < kHalf / 32; ++ch) {
         uint32_t a[32];
-        tmem_ld32(tDQ + ch * 32, a);
+        tmem_ld32(tacc + ch * 32, a);
         tmem_wait_ld();
-        if (ch == kD / 32 - 1) {
-          // every column is in registers: the accumulator columns may be overwritten
-          tc_fence_before();
-          mbar_arrive_warp(dq_empty);
-          if (warp == 8) TRACE(2, 11);
-        }
-        const float* af = reinterpret_cast<const float*>(a);
-#pragma unroll
-        for (int v = 0; v < 8; ++v)
-          red_add_v4(acc + ch * 32 + v * 4, af[4 * v], af[4 * v + 1], af[4 * v + 2], af[4 * v + 3]);
+        if (valid) store_row_16bit<kBf16>(dst + ch * 32, reinterpret_cast<const float*>(a), p.scale);
       }
     }
-  } else {
-    reg_dealloc<88>();
-    if (warp == 12) {
-      // =========================== MMA issuer ===========================
-      if (lane == 0) {
-        constexpr uint32_t idesc_st = umma_idesc(kBf16, false, false, 128, 128);  // S^T, dP^T
-        constexpr uint32_t idesc_acc = umma_idesc(kBf16, false, true, 128, kD);   // dV, dK (A from TMEM)
-        constexpr uint32_t idesc_dq = umma_idesc(kBf16, true, true, 128, kD);     // dQ (A, B MN-major)
-        const uint32_t tS = tmem_base + Cfg::kTmemS, tDP = tmem_base + Cfg::kTmemDP,
-                       tDV = tmem_base + Cfg::kTmemDV, tDK = tmem_base + Cfg::kTmemDK,
-                       tDQ = tmem_base + Cfg::kTmemDQ;
-        // Descriptors: fixed high word + start-address low word; K-major form (LBO unused) for
-        // the S^T / dP^T operands, MN-major form (LBO = next 64-column sub-tile) for the rest.
-        const UmmaDesc kK = umma_desc_split(smem_u32(sK), 16, 1024), kV = umma_desc_split(smem_u32(sV), 16, 1024),
-                       kQ = umma_desc_split(smem_u32(sQ), 16, 1024), kDO = umma_desc_split(smem_u32(sDO), 16, 1024);
-        const UmmaDesc mK = umma_desc_split(smem_u32(sK), kSubTileBytes, 1024),
-                       mQ = umma_desc_split(smem_u32(sQ), kSubTileBytes, 1024),
-                       mDO = umma_desc_split(smem_u32(sDO), kSubTileBytes, 1024),
-                       mDS = umma_desc_split(smem_u32(sDS), kSubTileBytes, 1024);
-        // D[128 x 128] = A[128 x kD] * B[128 x kD]^T, both K-major
-        auto issue_kmajor = [&](uint32_t d_tmem, const UmmaDesc& a, const UmmaDesc& b, uint32_t b_stage_lo) {
+  } else if (warp == 8) {
+    // =========================== MMA issuer ===========================
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = umma_idesc(kBf16, false, false, 128, 128);   // S, dP
+      constexpr uint32_t idesc_dq = umma_idesc(kBf16, false, true, 128, kD);    // dQ (A from TMEM, K MN-major)
+      const uint32_t tDP = tmem_base + kTmemDP, tDQ = tmem_base + kTmemDQ;
+      const UmmaDesc kQ = umma_desc_split(smem_u32(sQ), 16, 1024), kDO = umma_desc_split(smem_u32(sDO), 16, 1024),
+                     kK = umma_desc_split(smem_u32(sKV), 16, 1024),
+                     kV = umma_desc_split(smem_u32(sKV) + Cfg::kTileBytes, 16, 1024);
+      const UmmaDesc mK = umma_desc_split(smem_u32(sKV), kSubTileBytes, 1024);
+      auto issue_kmajor = [&](uint32_t d_tmem, const UmmaDesc& a, const UmmaDesc& bd, uint32_t b_stage_lo) {
 #pragma unroll
-          for (int kk = 0; kk < kD / 16; ++kk) {
-            const uint32_t off = umma_off((kk >> 2) * kSubTileBytes + (kk & 3) * 32);
-            if (kk == 0) umma_ss_fast<false>(d_tmem, a.lo + off, a.hi, b.lo + b_stage_lo + off, b.hi, idesc_st);
-            else         umma_ss_fast<true>(d_tmem, a.lo + off, a.hi, b.lo + b_stage_lo + off, b.hi, idesc_st);
-          }
-        };
-        // D[128 x kD] (+)= A^T-in-TMEM[128 x 128] * B[128 x kD] (B rows are the contraction index)
-        auto issue_ts = [&](uint32_t d_tmem, uint32_t a_tmem, const UmmaDesc& b, uint32_t b_stage_lo, bool acc) {
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
-            const uint32_t a_col = (kk < 4) ? kk * 8 : 64 + (kk - 4) * 8;
-            const uint32_t b_lo = b.lo + b_stage_lo + umma_off(kk * 2048);
-            if (kk == 0 && !acc) umma_ts_fast<false>(d_tmem, a_tmem + a_col, b_lo, b.hi, idesc_acc);
-            else                 umma_ts_fast<true>(d_tmem, a_tmem + a_col, b_lo, b.hi, idesc_acc);
-          }
-        };
-        B200FA_WAIT(kv_full, 0, 0x700);
-        B200FA_WAIT(&q_full[0], 0, 0x701);
-        tc_fence_after();
-        issue_kmajor(tS, kK, kQ, 0);
-        umma_commit(s_full);
-        B200FA_WAIT(&do_full[0], 0, 0x702);
-        tc_fence_after();
-        issue_kmajor(tDP, kV, kDO, 0);
-        umma_commit(dp_full);
-        for (int i = 0; i < steps; ++i) {
-          const int stage = i % Cfg::kStages;
-          const uint32_t stage_lo = stage * umma_off(Cfg::kTileBytes);
-          const bool has_next = (i + 1 < steps);
-          const int nstage = (i + 1) % Cfg::kStages;
-          const uint32_t nstage_lo = nstage * umma_off(Cfg::kTileBytes);
-          const uint32_t nphase = static_cast<uint32_t>(((i + 1) / Cfg::kStages) & 1);
-          // dV += P^T dO
-          TRACE(3, 20);
-          B200FA_WAIT(p_full, i & 1, 0x710);
-          tc_fence_after();
-          TRACE(3, 21);
-          issue_ts(tDV, tS, mDO, stage_lo, i > 0);
-          // S^T of the next step can start as soon as P^T has been consumed (in issue order)
-          if (has_next) {
-            B200FA_WAIT(&q_full[nstage], nphase, 0x711);
-            tc_fence_after();
-            issue_kmajor(tS, kK, kQ, nstage_lo);
-            umma_commit(s_full);
-          }
-          // dK += dS^T Q ; dQ = dS K
-          TRACE(3, 22);
-          B200FA_WAIT(ds_full, i & 1, 0x712);
-          tc_fence_after();
-          TRACE(3, 23);
-          issue_ts(tDK, tDP, mQ, stage_lo, i > 0);
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
-            const uint32_t off = umma_off(kk * 2048);
-            if (kk == 0) umma_ss_fast<false>(tDQ, mDS.lo + off, mDS.hi, mK.lo + off, mK.hi, idesc_dq);
-            else         umma_ss_fast<true>(tDQ, mDS.lo + off, mDS.hi, mK.lo + off, mK.hi, idesc_dq);
-          }
-          umma_commit(dq_full);
-          umma_commit(&qdo_empty[stage]);
-          TRACE(3, 24);
-          if (has_next) {
-            B200FA_WAIT(&do_full[nstage], nphase, 0x713);
-            B200FA_WAIT(dq_empty, i & 1, 0x714);
-            tc_fence_after();
-            TRACE(3, 25);
-            issue_kmajor(tDP, kV, kDO, nstage_lo);
-            umma_commit(dp_full);
-          }
+        for (int kk = 0; kk < kD / 16; ++kk) {
+          const uint32_t off = umma_off((kk >> 2) * kSubTileBytes + (kk & 3) * 32);
+          if (kk == 0) umma_ss_fast<false>(d_tmem, a.lo + off, a.hi, bd.lo + b_stage_lo + off, bd.hi, idesc_s);
+          else         umma_ss_fast<true>(d_tmem, a.lo + off, a.hi, bd.lo + b_stage_lo + off, bd.hi, idesc_s);
         }
-        umma_commit(dkdv_full);
+      };
+      constexpr uint32_t kStageLo = umma_off(2 * Cfg::kTileBytes);
+      // prologue: S_0, dP_0, S_1
+      B200FA_WAIT(qdo_full, 0, 0xa00);
+      B200FA_WAIT(&kv_full[0], 0, 0xa01);
+      tc_fence_after();
+      issue_kmajor(tmem_base + kTmemS, kQ, kK, 0);
+      umma_commit(&s_full[0]);
+      issue_kmajor(tDP, kDO, kV, 0);
+      umma_commit(dp_full);
+      if (n_tiles > 1) {
+        B200FA_WAIT(&kv_full[1], 0, 0xa02);
+        tc_fence_after();
+        issue_kmajor(tmem_base + kTmemS + 128, kQ, kK, kStageLo);
+        umma_commit(&s_full[1]);
       }
-    } else if (warp == 13) {
-      // =========================== TMA producer ===========================
-      if (lane == 0) {
-        auto load_tile = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int srow, int head) {
-#pragma unroll
-          for (int cs = 0; cs < Cfg::kSub; ++cs) tma_load_4d(dst + cs * kSubTileBytes, map, bar, cs * 64, srow, head, b);
-        };
-        mbar_arrive_expect_tx(kv_full, 2 * Cfg::kTileBytes);
-        load_tile(&mapK, sK, kv_full, n0, hk);
-        load_tile(&mapV, sV, kv_full, n0, hk);
-        for (int i = 0; i < steps; ++i) {
-          const int stage = i % Cfg::kStages;
-          const int g = i / per_head;
-          const int m_tile = m_start + i % per_head;
-          const int h = hk * group + g;
-          if (i >= Cfg::kStages) {
-            B200FA_WAIT(&qdo_empty[stage], ((i / Cfg::kStages) - 1) & 1, 0x800);
-          }
-          const int64_t stat_off = (static_cast<int64_t>(b) * p.Hq + h) * p.Spad + m_tile * kTile;
-          float* st = sStat + stage * 256;
-          mbar_arrive_expect_tx(&q_full[stage], Cfg::kTileBytes + 512);
-          load_tile(&mapQ, sQ + stage * Cfg::kTileBytes, &q_full[stage], m_tile * kTile, h);
-          bulk_load_1d(st, p.lse_log2 + stat_off, 512, &q_full[stage]);
-          mbar_arrive_expect_tx(&do_full[stage], Cfg::kTileBytes + 512);
-          load_tile(&mapDO, sDO + stage * Cfg::kTileBytes, &do_full[stage], m_tile * kTile, h);
-          bulk_load_1d(st + 128, p.dpsum + stat_off, 512, &do_full[stage]);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int stage = j & 1;
+        const uint32_t stage_lo = stage * kStageLo;
+        const uint32_t tSj = tmem_base + kTmemS + stage * 128;
+        // compute has read dP_j and written dS_j over S_j
+        B200FA_WAIT(ds_full, j & 1, 0xa10);
+        tc_fence_after();
+        TRACE(3, 21);
+        if (j + 1 < n_tiles) {
+          // dP of the next tile first, so the compute warps get it while dQ runs
+          issue_kmajor(tDP, kDO, kV, (stage ^ 1) * kStageLo);
+          umma_commit(dp_full);
         }
+        // dQ += dS_j K_j   (A = 16-bit dS in the S_j columns, B = K_j rows as the contraction index)
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t a_col = (kk < 4) ? kk * 8 : 64 + (kk - 4) * 8;
+          const uint32_t b_lo = mK.lo + stage_lo + umma_off(kk * 2048);
+          if (kk == 0 && j == 0) umma_ts_fast<false>(tDQ, tSj + a_col, b_lo, mK.hi, idesc_dq);
+          else                   umma_ts_fast<true>(tDQ, tSj + a_col, b_lo, mK.hi, idesc_dq);
+        }
+        umma_commit(&kv_empty[stage]);
+        if (j + 2 < n_tiles) {
+          // S of tile j+2 re-uses this K/V stage and this S buffer
+          B200FA_WAIT(&kv_full[stage], ((j + 2) >> 1) & 1, 0xa11);
+          tc_fence_after();
+          issue_kmajor(tSj, kQ, kK, stage_lo);
+          umma_commit(&s_full[stage]);
+        }
+      }
+      umma_commit(acc_full);
+    }
+  } else if (warp == 9) {
+    // =========================== TMA producer ===========================
+    if (lane == 0) {
+      auto load_tile = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int srow, int head) {
+#pragma unroll
+        for (int cs = 0; cs < Cfg::kSub; ++cs) tma_load_4d(dst + cs * kSubTileBytes, map, bar, cs * 64, srow, head, b);
+      };
+      mbar_arrive_expect_tx(qdo_full, 2 * Cfg::kTileBytes);
+      load_tile(&mapQ, sQ, qdo_full, m0, h);
+      load_tile(&mapDO, sDO, qdo_full, m0, h);
+      for (int j = 0; j < n_tiles; ++j) {
+        const int stage = j & 1;
+        if (j >= Cfg::kStages) {
+          B200FA_WAIT(&kv_empty[stage], ((j >> 1) - 1) & 1, 0xb00);
+        }
+        uint8_t* k_dst = sKV + stage * 2 * Cfg::kTileBytes;
+        mbar_arrive_expect_tx(&kv_full[stage], 2 * Cfg::kTileBytes);
+        load_tile(&mapK, k_dst, &kv_full[stage], j * kTile, hk);
+        load_tile(&mapV, k_dst + Cfg::kTileBytes, &kv_full[stage], j * kTile, hk);
       }
     }
   }
 
 teardown:
-#undef B200FA_WAIT
   tc_fence_before();
   __syncthreads();
-  if (warp == 12) {
+  if (warp == 8) {
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
 }
+#undef B200FA_WAIT
 
 // ------------------------------------------------------------------------------------------
-// preprocess: dpsum = rowsum(dO * O), lse2 = lse * log2(e), zero the fp32 dQ accumulator.
-// Rows in [S, Spad) get lse2 = +inf and dpsum = 0 so their probabilities vanish.
-// One row per group of D/8 lanes; every lane moves 16 bytes of O and of dO.
+// preprocess: dpsum = rowsum(dO * O), lse2 = lse * log2(e), per (b, h, row), padded to a
+// multiple of 128 rows.  Rows in [S, Spad) get lse2 = +inf and dpsum = 0 so their
+// probabilities vanish.  One row per group of D/8 lanes; every lane moves 16 bytes of O and dO.
 // ------------------------------------------------------------------------------------------
 template <int kD, bool kBf16>
 __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const BwdParams p) {
@@ -489,69 +680,41 @@ __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const BwdParams p) 
     p.lse_log2[row_global] =
         (s < p.S) ? p.lse[(static_cast<int64_t>(b) * p.Hq + h) * p.S + s] * 1.4426950408889634f : INFINITY;
   }
-  float4* z = reinterpret_cast<float4*>(p.dq_accum + row_global * kD + li * 8);
-  z[0] = make_float4(0.f, 0.f, 0.f, 0.f);
-  z[1] = make_float4(0.f, 0.f, 0.f, 0.f);
-}
-
-// convert: dQ = (fp32 accumulator * scale) rounded to the 16-bit type; 8 elements per thread.
-template <int kD, bool kBf16>
-__global__ void __launch_bounds__(256) bwd_convert_kernel(const BwdParams p) {
-  constexpr int kVecPerRow = kD / 8;
-  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const int64_t total = static_cast<int64_t>(p.B) * p.Hq * p.S * kVecPerRow;
-  if (idx >= total) return;
-  const int vec = static_cast<int>(idx % kVecPerRow);
-  const int64_t row = idx / kVecPerRow;
-  const int s = static_cast<int>(row % p.S);
-  const int64_t bh = row / p.S;
-  const int h = static_cast<int>(bh % p.Hq);
-  const int b = static_cast<int>(bh / p.Hq);
-  const float4* src = reinterpret_cast<const float4*>(p.dq_accum + (bh * p.Spad + s) * kD + vec * 8);
-  const float4 a = src[0], c = src[1];
-  uint4 w;
-  w.x = pack2<kBf16>(a.x * p.scale, a.y * p.scale);
-  w.y = pack2<kBf16>(a.z * p.scale, a.w * p.scale);
-  w.z = pack2<kBf16>(c.x * p.scale, c.y * p.scale);
-  w.w = pack2<kBf16>(c.z * p.scale, c.w * p.scale);
-  uint16_t* dst = reinterpret_cast<uint16_t*>(p.dq.ptr) +
-                  (static_cast<int64_t>(b) * p.dq.sb + static_cast<int64_t>(h) * p.dq.sh +
-                   static_cast<int64_t>(s) * p.dq.ss) + vec * 8;
-  *reinterpret_cast<uint4*>(dst) = w;
 }
 
 template <int kD, bool kBf16, bool kCausal>
 cudaError_t launch_one(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mdo,
                        const BwdParams& p, cudaStream_t stream) {
   using Cfg = BwdCfg<kD>;
-  constexpr int kRowsPerWarp = 32 / (kD / 8);
-  const int64_t total_rows = static_cast<int64_t>(p.B) * p.Hq * p.Spad;
-  const int64_t pre_warps = (total_rows + kRowsPerWarp - 1) / kRowsPerWarp;
   cudaError_t e = cudaSuccess;
   if (p.parts & 1) {
+    constexpr int kRowsPerWarp = 32 / (kD / 8);
+    const int64_t total_rows = static_cast<int64_t>(p.B) * p.Hq * p.Spad;
+    const int64_t pre_warps = (total_rows + kRowsPerWarp - 1) / kRowsPerWarp;
     bwd_preprocess_kernel<kD, kBf16><<<static_cast<unsigned>((pre_warps + 7) / 8), 256, 0, stream>>>(p);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }
-
-  auto kern = bwd_kernel<kD, kBf16, kCausal>;
+  auto k1 = bwd_dkdv_kernel<kD, kBf16, kCausal>;
+  auto k2 = bwd_dq_kernel<kD, kBf16, kCausal>;
   static bool attr_set[16] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 16 && !attr_set[dev]) {
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
+  const int tiles = (p.S + kTile - 1) / kTile;
   if (p.parts & 2) {
-    dim3 grid((p.S + kTile - 1) / kTile, p.Hkv, p.B);
-    kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(mq, mk, mv, mdo, p);
+    k1<<<dim3(tiles, p.Hkv, p.B), kThreads, Cfg::kSmemBytes, stream>>>(mq, mk, mv, mdo, p);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }
   if (p.parts & 4) {
-    const int64_t total_vec = static_cast<int64_t>(p.B) * p.Hq * p.S * (kD / 8);
-    bwd_convert_kernel<kD, kBf16><<<static_cast<unsigned>((total_vec + 255) / 256), 256, 0, stream>>>(p);
+    k2<<<dim3(tiles, p.Hq, p.B), kThreads, Cfg::kSmemBytes, stream>>>(mq, mk, mv, mdo, p);
     e = cudaGetLastError();
   }
   return e;

@@ -28,13 +28,13 @@ struct BwdParams {
   const float* lse;  // (B, Hq, S) fp32 contiguous (natural log)
   float* dpsum;      // workspace: (B, Hq, Spad) rowsum(dO * O)
   float* lse_log2;   // workspace: (B, Hq, Spad) lse * log2(e)
-  float* dq_accum;   // workspace: (B, Hq, Spad, D) fp32
+  float* dq_accum;   // unused (kept for layout stability): dQ accumulates in tensor memory
   int B, Hq, Hkv, S, Spad, D;
   int causal;
   float scale;
   float scale_log2;
   uint32_t* status;
-  int parts;  // bit 0 preprocess, bit 1 main kernel, bit 2 dQ convert (7 = the whole backward)
+  int parts;  // bit 0 preprocess, bit 1 dK/dV kernel, bit 2 dQ kernel (7 = the whole backward)
 };
 
 // dtype tags shared with the C header

@@ -54,8 +54,11 @@ struct BwdCfg {
   static constexpr int kOffStream = 2 * kTileBytes;
   static constexpr int kOffStat = kOffStream + kStages * 2 * kTileBytes;  // [stage][lse2|dpsum][128] fp32
   static constexpr int kOffBars = kOffStat + kStages * 2 * 128 * 4;
-  static constexpr int kNumBars = 16;
-  static constexpr int kSmemBytes = kOffBars + kNumBars * 8 + 16;
+  static constexpr int kNumBars = 20;
+  // the dQ kernel keeps 2 resident + 3 K + 2 V tiles and no per-stage statistics
+  static constexpr int kOffDqBars = 7 * kTileBytes;
+  static constexpr int kSmemBytes =
+      (kOffBars > kOffDqBars ? kOffBars : kOffDqBars) + kNumBars * 8 + 16;
 };
 
 template <bool kBf16>
@@ -390,14 +393,20 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
   using Cfg = BwdCfg<kD>;
   constexpr int kTmemS = 0, kTmemDP = 256, kTmemDQ = 384;
   extern __shared__ __align__(1024) uint8_t smem[];
+  // K_j is needed twice, a whole step apart (S_j, then dQ += dS_j K_j); V_j only once (dP_j).
+  // Separate rings - three K slots, two V slots - keep a full step of TMA prefetch ahead of
+  // the tensor pipe within the shared-memory budget.
   uint8_t* sQ = smem + Cfg::kOffResident;
   uint8_t* sDO = sQ + Cfg::kTileBytes;
-  uint8_t* sKV = smem + Cfg::kOffStream;          // stage s: K at sKV + s * 2 * tile, V right behind
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBars);
+  uint8_t* sK = smem + Cfg::kOffStream;                       // [3] tiles
+  uint8_t* sV = sK + 3 * Cfg::kTileBytes;                     // [2] tiles
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kOffDqBars);
   uint64_t* qdo_full = bars;                       // [1]
-  uint64_t* kv_full = qdo_full + 1;                // [kStages]
-  uint64_t* kv_empty = kv_full + Cfg::kStages;     // [kStages]
-  uint64_t* s_full = kv_empty + Cfg::kStages;      // [2]  S buffer ready
+  uint64_t* k_full = qdo_full + 1;                 // [3]
+  uint64_t* k_empty = k_full + 3;                  // [3]
+  uint64_t* v_full = k_empty + 3;                  // [2]
+  uint64_t* v_empty = v_full + 2;                  // [2]
+  uint64_t* s_full = v_empty + 2;                  // [2]  S buffer ready
   uint64_t* dp_full = s_full + 2;                  // dP ready
   uint64_t* ds_full = dp_full + 1;                 // dS written, dP consumed (8 warp arrivals)
   uint64_t* acc_full = ds_full + 1;                // dQ complete
@@ -423,9 +432,13 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
   }
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
-    for (int i = 0; i < Cfg::kStages; ++i) {
-      mbar_init(&kv_full[i], 1);
-      mbar_init(&kv_empty[i], 1);
+    for (int i = 0; i < 3; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
     }
     mbar_init(&s_full[0], 1);
     mbar_init(&s_full[1], 1);
@@ -533,61 +546,68 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
       constexpr uint32_t idesc_dq = umma_idesc(kBf16, false, true, 128, kD);    // dQ (A from TMEM, K MN-major)
       const uint32_t tDP = tmem_base + kTmemDP, tDQ = tmem_base + kTmemDQ;
       const UmmaDesc kQ = umma_desc_split(smem_u32(sQ), 16, 1024), kDO = umma_desc_split(smem_u32(sDO), 16, 1024),
-                     kK = umma_desc_split(smem_u32(sKV), 16, 1024),
-                     kV = umma_desc_split(smem_u32(sKV) + Cfg::kTileBytes, 16, 1024);
-      const UmmaDesc mK = umma_desc_split(smem_u32(sKV), kSubTileBytes, 1024);
-      auto issue_kmajor = [&](uint32_t d_tmem, const UmmaDesc& a, const UmmaDesc& bd, uint32_t b_stage_lo) {
+                     kK = umma_desc_split(smem_u32(sK), 16, 1024), kV = umma_desc_split(smem_u32(sV), 16, 1024);
+      const UmmaDesc mK = umma_desc_split(smem_u32(sK), kSubTileBytes, 1024);
+      auto issue_kmajor = [&](uint32_t d_tmem, const UmmaDesc& a, const UmmaDesc& bd, uint32_t b_slot_lo) {
 #pragma unroll
         for (int kk = 0; kk < kD / 16; ++kk) {
           const uint32_t off = umma_off((kk >> 2) * kSubTileBytes + (kk & 3) * 32);
-          if (kk == 0) umma_ss_fast<false>(d_tmem, a.lo + off, a.hi, bd.lo + b_stage_lo + off, bd.hi, idesc_s);
-          else         umma_ss_fast<true>(d_tmem, a.lo + off, a.hi, bd.lo + b_stage_lo + off, bd.hi, idesc_s);
+          if (kk == 0) umma_ss_fast<false>(d_tmem, a.lo + off, a.hi, bd.lo + b_slot_lo + off, bd.hi, idesc_s);
+          else         umma_ss_fast<true>(d_tmem, a.lo + off, a.hi, bd.lo + b_slot_lo + off, bd.hi, idesc_s);
         }
       };
-      constexpr uint32_t kStageLo = umma_off(2 * Cfg::kTileBytes);
+      constexpr uint32_t kTileLo = umma_off(Cfg::kTileBytes);
       // prologue: S_0, dP_0, S_1
       B200FA_WAIT(qdo_full, 0, 0xa00);
-      B200FA_WAIT(&kv_full[0], 0, 0xa01);
+      B200FA_WAIT(&k_full[0], 0, 0xa01);
       tc_fence_after();
       issue_kmajor(tmem_base + kTmemS, kQ, kK, 0);
       umma_commit(&s_full[0]);
+      B200FA_WAIT(&v_full[0], 0, 0xa03);
+      tc_fence_after();
       issue_kmajor(tDP, kDO, kV, 0);
       umma_commit(dp_full);
+      umma_commit(&v_empty[0]);
       if (n_tiles > 1) {
-        B200FA_WAIT(&kv_full[1], 0, 0xa02);
+        B200FA_WAIT(&k_full[1], 0, 0xa02);
         tc_fence_after();
-        issue_kmajor(tmem_base + kTmemS + 128, kQ, kK, kStageLo);
+        issue_kmajor(tmem_base + kTmemS + 128, kQ, kK, kTileLo);
         umma_commit(&s_full[1]);
       }
+      int kslot = 0;  // ring slot of K_j
       for (int j = 0; j < n_tiles; ++j) {
-        const int stage = j & 1;
-        const uint32_t stage_lo = stage * kStageLo;
-        const uint32_t tSj = tmem_base + kTmemS + stage * 128;
+        const int buf = j & 1;
+        const uint32_t tSj = tmem_base + kTmemS + buf * 128;
+        const int k2slot = (kslot == 0) ? 2 : kslot - 1;   // slot of K_{j+2} = (j + 2) % 3
+        if (j + 1 < n_tiles) { B200FA_WAIT(&v_full[buf ^ 1], ((j + 1) >> 1) & 1, 0xa12); }
         // compute has read dP_j and written dS_j over S_j
         B200FA_WAIT(ds_full, j & 1, 0xa10);
         tc_fence_after();
         TRACE(3, 21);
         if (j + 1 < n_tiles) {
           // dP of the next tile first, so the compute warps get it while dQ runs
-          issue_kmajor(tDP, kDO, kV, (stage ^ 1) * kStageLo);
+          issue_kmajor(tDP, kDO, kV, (buf ^ 1) * kTileLo);
           umma_commit(dp_full);
+          umma_commit(&v_empty[buf ^ 1]);
         }
         // dQ += dS_j K_j   (A = 16-bit dS in the S_j columns, B = K_j rows as the contraction index)
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t a_col = (kk < 4) ? kk * 8 : 64 + (kk - 4) * 8;
-          const uint32_t b_lo = mK.lo + stage_lo + umma_off(kk * 2048);
+          const uint32_t b_lo = mK.lo + kslot * kTileLo + umma_off(kk * 2048);
           if (kk == 0 && j == 0) umma_ts_fast<false>(tDQ, tSj + a_col, b_lo, mK.hi, idesc_dq);
           else                   umma_ts_fast<true>(tDQ, tSj + a_col, b_lo, mK.hi, idesc_dq);
         }
-        umma_commit(&kv_empty[stage]);
+        umma_commit(&k_empty[kslot]);
         if (j + 2 < n_tiles) {
-          // S of tile j+2 re-uses this K/V stage and this S buffer
-          B200FA_WAIT(&kv_full[stage], ((j + 2) >> 1) & 1, 0xa11);
+          // S of tile j+2 re-uses this S buffer
+          B200FA_WAIT(&k_full[k2slot], static_cast<uint32_t>(((j + 2) / 3) & 1), 0xa11);
           tc_fence_after();
-          issue_kmajor(tSj, kQ, kK, stage_lo);
-          umma_commit(&s_full[stage]);
+          TRACE(3, 22);
+          issue_kmajor(tSj, kQ, kK, k2slot * kTileLo);
+          umma_commit(&s_full[buf]);
         }
+        if (++kslot == 3) kslot = 0;
       }
       umma_commit(acc_full);
     }
@@ -601,15 +621,18 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
       mbar_arrive_expect_tx(qdo_full, 2 * Cfg::kTileBytes);
       load_tile(&mapQ, sQ, qdo_full, m0, h);
       load_tile(&mapDO, sDO, qdo_full, m0, h);
+      int kslot = 0;
       for (int j = 0; j < n_tiles; ++j) {
-        const int stage = j & 1;
-        if (j >= Cfg::kStages) {
-          B200FA_WAIT(&kv_empty[stage], ((j >> 1) - 1) & 1, 0xb00);
-        }
-        uint8_t* k_dst = sKV + stage * 2 * Cfg::kTileBytes;
-        mbar_arrive_expect_tx(&kv_full[stage], 2 * Cfg::kTileBytes);
-        load_tile(&mapK, k_dst, &kv_full[stage], j * kTile, hk);
-        load_tile(&mapV, k_dst + Cfg::kTileBytes, &kv_full[stage], j * kTile, hk);
+        if (j >= 3) { B200FA_WAIT(&k_empty[kslot], static_cast<uint32_t>((j / 3 - 1) & 1), 0xb00); }
+        TRACE(4, 30);
+        mbar_arrive_expect_tx(&k_full[kslot], Cfg::kTileBytes);
+        load_tile(&mapK, sK + kslot * Cfg::kTileBytes, &k_full[kslot], j * kTile, hk);
+        const int vslot = j & 1;
+        if (j >= 2) { B200FA_WAIT(&v_empty[vslot], ((j >> 1) - 1) & 1, 0xb01); }
+        TRACE(4, 31);
+        mbar_arrive_expect_tx(&v_full[vslot], Cfg::kTileBytes);
+        load_tile(&mapV, sV + vslot * Cfg::kTileBytes, &v_full[vslot], j * kTile, hk);
+        if (++kslot == 3) kslot = 0;
       }
     }
   }

@@ -19,8 +19,8 @@
 // instead of 5), every accumulator lives in TMEM, and the results are deterministic.
 //
 // Both kernels: warps 0-3 and 4-7 are two compute warpgroups that split the 128 score
-// columns of a tile in halves (thread <-> TMEM lane), warp 8 issues the MMAs, warp 9 drives
-// TMA, warps 10-11 idle.
+// columns of a tile in halves (thread <-> TMEM lane), warps 8 and 9 each issue one of the two
+// independent MMA chains, warp 10 drives TMA, warp 11 idles.
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -52,7 +52,8 @@ struct BwdCfg {
   // resident pair of tiles, then kStages pairs of streamed tiles, then per-stage row statistics
   static constexpr int kOffResident = 0;
   static constexpr int kOffStream = 2 * kTileBytes;
-  static constexpr int kOffStat = kOffStream + kStages * 2 * kTileBytes;  // [stage][lse2|dpsum][128] fp32
+  static constexpr int kOffP = kOffStream + kStages * 2 * kTileBytes;     // dK/dV kernel: 128 x 128 16-bit P^T tile
+  static constexpr int kOffStat = kOffP + 128 * 128 * 2;                  // [stage][lse2|dpsum][128] fp32
   static constexpr int kOffBars = kOffStat + kStages * 2 * 128 * 4;
   static constexpr int kNumBars = 20;
   // the dQ kernel keeps 2 resident + 3 K + 2 V tiles and no per-stage statistics
@@ -80,8 +81,9 @@ __device__ __forceinline__ void store_row_16bit(uint16_t* dst, const float* v, f
 // ------------------------------------------------------------------------------------------
 // dK / dV kernel.  One CTA = one 128-row K/V tile of one (batch, kv head); it walks every
 // query tile at or below the causal diagonal for every query head of the GQA group.
-// TMEM columns: [0,128) S^T, overwritten in place by 16-bit P^T; [128,256) dP^T, overwritten
-// by 16-bit dS^T; then dV and dK accumulators.
+// TMEM columns: [0,128) S^T; [128,256) dP^T, overwritten by 16-bit dS^T (the A operand of the
+// dK MMA); then the dV and dK accumulators.  16-bit P^T goes through shared memory instead, so
+// S^T of the next step can be issued while the exponentials of this step are still running.
 // ------------------------------------------------------------------------------------------
 template <int kD, bool kBf16, bool kCausal>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -94,6 +96,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   uint8_t* sK = smem + Cfg::kOffResident;
   uint8_t* sV = sK + Cfg::kTileBytes;
   uint8_t* sQ = smem + Cfg::kOffStream;                          // stage s: sQ + s * 2 * tile, dO right behind
+  uint8_t* sP = smem + Cfg::kOffP;                               // 16-bit P^T, [key row][query column], swizzled
   float* sStat = reinterpret_cast<float*>(smem + Cfg::kOffStat);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kOffBars);
   uint64_t* kv_full = bars;                        // [1]
@@ -105,6 +108,8 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   uint64_t* p_full = dp_full + 1;                  // P^T written  (8 warp arrivals)
   uint64_t* ds_full = p_full + 1;                  // dS^T written (8 warp arrivals)
   uint64_t* acc_full = ds_full + 1;                // dK, dV complete
+  uint64_t* s_free = acc_full + 1;                 // S^T read into registers (8 warp arrivals)
+  uint64_t* p_empty = s_free + 1;                  // dV MMA has consumed the P^T tile
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::kNumBars);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -133,13 +138,15 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     for (int i = 0; i < Cfg::kStages; ++i) {
       mbar_init(&q_full[i], 1);
       mbar_init(&do_full[i], 1);
-      mbar_init(&qdo_empty[i], 1);
+      mbar_init(&qdo_empty[i], 2);   // both MMA-issuing lanes release a stage
     }
     mbar_init(s_full, 1);
     mbar_init(dp_full, 1);
     mbar_init(p_full, 8);   // one elected arrival per compute warp
     mbar_init(ds_full, 8);
-    mbar_init(acc_full, 1);
+    mbar_init(acc_full, 2);        // both MMA-issuing lanes
+    mbar_init(s_free, 8);
+    mbar_init(p_empty, 1);
     *abort_flag = 0;
     fence_mbar_init();
     fence_proxy_async_smem();
@@ -148,7 +155,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
-  if (warp == 9 && lane == 0) {
+  if (warp == 10 && lane == 0) {
     tma_prefetch_desc(&mapQ);
     tma_prefetch_desc(&mapK);
     tma_prefetch_desc(&mapV);
@@ -167,47 +174,58 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     const uint32_t tS = tmem_base + lane_off + kTmemS + wg * 64;
     const uint32_t tDP = tmem_base + lane_off + kTmemDP + wg * 64;
     const float c = p.scale_log2;
+    // this thread's 128-byte row of the 128-byte-swizzled P^T tile (64 query columns)
+    uint8_t* p_row = sP + wg * kSubTileBytes + j * 128;
     for (int i = 0; i < steps; ++i) {
       const int stage = i % Cfg::kStages;
       const uint32_t ring_phase = static_cast<uint32_t>((i / Cfg::kStages) & 1);
       const int m_tile = m_start + i % per_head;
       const float4* lse2 = reinterpret_cast<const float4*>(sStat + stage * 256 + wg * 64);
       const float4* dps = lse2 + 32;
-      // ---- P^T = exp2(S^T * c - lse2)
+      // ---- P^T = exp2(S^T * c - lse2).  S^T is pulled into registers in one go and released
+      // at once, so the MMA warp can start S^T of the next step while the exponentials run;
+      // P^T goes to shared memory (the A operand of dV += P^T dO) instead of back over S^T.
       B200FA_WAIT(s_full, i & 1, 0x500);
       // lse2 rode in with the Q tile; observing its barrier directly makes the bulk copy visible here
       B200FA_WAIT(&q_full[stage], ring_phase, 0x501);
       tc_fence_after();
       if ((warp & 3) == 0) TRACE(wg, 1);
       float pf[64];
-#pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
-        uint32_t s[32];
-        tmem_ld32(tS + ch * 32, s);
+      {
+        uint32_t* s = reinterpret_cast<uint32_t*>(pf);
+        tmem_ld32(tS, s);
+        tmem_ld32(tS + 32, s + 32);
         tmem_wait_ld();
-        const float* sf = reinterpret_cast<const float*>(s);
-#pragma unroll
-        for (int e4 = 0; e4 < 8; ++e4) {
-          const float4 l4 = lse2[ch * 8 + e4];
-          pf[ch * 32 + e4 * 4 + 0] = ex2_approx(fmaf(sf[e4 * 4 + 0], c, -l4.x));
-          pf[ch * 32 + e4 * 4 + 1] = ex2_approx(fmaf(sf[e4 * 4 + 1], c, -l4.y));
-          pf[ch * 32 + e4 * 4 + 2] = ex2_approx(fmaf(sf[e4 * 4 + 2], c, -l4.z));
-          pf[ch * 32 + e4 * 4 + 3] = ex2_approx(fmaf(sf[e4 * 4 + 3], c, -l4.w));
-        }
-        if (kCausal && m_tile == n_tile) {
-          // on the diagonal tile, query column q sees key row j only if j <= q
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            if (j > wg * 64 + ch * 32 + e) pf[ch * 32 + e] = 0.f;
-          }
-        }
-        uint32_t pk[16];
-#pragma unroll
-        for (int e = 0; e < 16; ++e) pk[e] = pack2<kBf16>(pf[ch * 32 + 2 * e], pf[ch * 32 + 2 * e + 1]);
-        tmem_st16(tS + ch * 16, pk);
+        tc_fence_before();
+        mbar_arrive_warp(s_free);
       }
-      tmem_wait_st();
-      tc_fence_before();
+#pragma unroll
+      for (int e4 = 0; e4 < 16; ++e4) {
+        const float4 l4 = lse2[e4];
+        pf[e4 * 4 + 0] = ex2_approx(fmaf(pf[e4 * 4 + 0], c, -l4.x));
+        pf[e4 * 4 + 1] = ex2_approx(fmaf(pf[e4 * 4 + 1], c, -l4.y));
+        pf[e4 * 4 + 2] = ex2_approx(fmaf(pf[e4 * 4 + 2], c, -l4.z));
+        pf[e4 * 4 + 3] = ex2_approx(fmaf(pf[e4 * 4 + 3], c, -l4.w));
+      }
+      if (kCausal && m_tile == n_tile) {
+        // on the diagonal tile, query column q sees key row j only if j <= q
+#pragma unroll
+        for (int e = 0; e < 64; ++e) {
+          if (j > wg * 64 + e) pf[e] = 0.f;
+        }
+      }
+      // the previous step's dV MMA must have finished reading the P^T tile
+      if (i > 0) { B200FA_WAIT(p_empty, (i - 1) & 1, 0x502); }
+#pragma unroll
+      for (int chunk = 0; chunk < 8; ++chunk) {
+        uint4 w;
+        w.x = pack2<kBf16>(pf[chunk * 8 + 0], pf[chunk * 8 + 1]);
+        w.y = pack2<kBf16>(pf[chunk * 8 + 2], pf[chunk * 8 + 3]);
+        w.z = pack2<kBf16>(pf[chunk * 8 + 4], pf[chunk * 8 + 5]);
+        w.w = pack2<kBf16>(pf[chunk * 8 + 6], pf[chunk * 8 + 7]);
+        *reinterpret_cast<uint4*>(p_row + ((chunk ^ (j & 7)) << 4)) = w;
+      }
+      fence_proxy_async_smem();
       mbar_arrive_warp(p_full);
       if ((warp & 3) == 0) TRACE(wg, 2);
       // ---- dS^T = P^T * (dP^T - dpsum)
@@ -263,19 +281,24 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         }
       }
     }
-  } else if (warp == 8) {
-    // =========================== MMA issuer ===========================
+  } else if (warp == 8 || warp == 9) {
+    // =========================== MMA issuers ===========================
+    // A tcgen05.mma only issues once the tensor pipe has room, so an issuing lane is stalled
+    // for about as long as its MMAs run.  The S^T -> P^T -> dV chain and the dP^T -> dS^T -> dK
+    // chain are independent, so each gets its own lane: neither waits behind the other's
+    // operands.  Warp 8: S^T of the next step and dV.  Warp 9: dK and dP^T of the next step.
     if (lane == 0) {
       constexpr uint32_t idesc_st = umma_idesc(kBf16, false, false, 128, 128);  // S^T, dP^T
-      constexpr uint32_t idesc_acc = umma_idesc(kBf16, false, true, 128, kD);   // dV, dK (A from TMEM)
+      constexpr uint32_t idesc_acc = umma_idesc(kBf16, false, true, 128, kD);   // dV (A in smem), dK (A in TMEM)
       const uint32_t tS = tmem_base + kTmemS, tDP = tmem_base + kTmemDP, tDV = tmem_base + kTmemDV,
                      tDK = tmem_base + kTmemDK;
       // Descriptors: fixed high word + start-address low word.  K-major form for the S^T / dP^T
-      // operands, MN-major form (LBO = next 64-column sub-tile) when Q / dO are the B operand
-      // of an accumulating MMA.
+      // operands and the P^T tile, MN-major form (LBO = next 64-column sub-tile) when Q / dO
+      // are the B operand of an accumulating MMA.
       const UmmaDesc kK = umma_desc_split(smem_u32(sK), 16, 1024), kV = umma_desc_split(smem_u32(sV), 16, 1024),
                      kQ = umma_desc_split(smem_u32(sQ), 16, 1024),
-                     kDO = umma_desc_split(smem_u32(sQ) + Cfg::kTileBytes, 16, 1024);
+                     kDO = umma_desc_split(smem_u32(sQ) + Cfg::kTileBytes, 16, 1024),
+                     kP = umma_desc_split(smem_u32(sP), 16, 1024);
       const UmmaDesc mQ = umma_desc_split(smem_u32(sQ), kSubTileBytes, 1024),
                      mDO = umma_desc_split(smem_u32(sQ) + Cfg::kTileBytes, kSubTileBytes, 1024);
       // D[128 x 128] = A[128 x kD] * B[128 x kD]^T, both K-major
@@ -287,58 +310,76 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
           else         umma_ss_fast<true>(d_tmem, a.lo + off, a.hi, bd.lo + b_stage_lo + off, bd.hi, idesc_st);
         }
       };
-      // D[128 x kD] (+)= A-in-TMEM[128 x 128] * B[128 x kD] (B rows are the contraction index)
-      auto issue_ts = [&](uint32_t d_tmem, uint32_t a_tmem, const UmmaDesc& bd, uint32_t b_stage_lo, bool first) {
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t a_col = (kk < 4) ? kk * 8 : 64 + (kk - 4) * 8;
-          const uint32_t b_lo = bd.lo + b_stage_lo + umma_off(kk * 2048);
-          if (kk == 0 && first) umma_ts_fast<false>(d_tmem, a_tmem + a_col, b_lo, bd.hi, idesc_acc);
-          else                  umma_ts_fast<true>(d_tmem, a_tmem + a_col, b_lo, bd.hi, idesc_acc);
-        }
-      };
       constexpr uint32_t kStageLo = umma_off(2 * Cfg::kTileBytes);
-      B200FA_WAIT(kv_full, 0, 0x700);
-      B200FA_WAIT(&q_full[0], 0, 0x701);
-      tc_fence_after();
-      issue_kmajor(tS, kK, kQ, 0);
-      umma_commit(s_full);
-      B200FA_WAIT(&do_full[0], 0, 0x702);
-      tc_fence_after();
-      issue_kmajor(tDP, kV, kDO, 0);
-      umma_commit(dp_full);
-      for (int i = 0; i < steps; ++i) {
-        const int stage = i % Cfg::kStages;
-        const uint32_t stage_lo = stage * kStageLo;
-        const bool has_next = (i + 1 < steps);
-        const int nstage = (i + 1) % Cfg::kStages;
-        const uint32_t nphase = static_cast<uint32_t>(((i + 1) / Cfg::kStages) & 1);
-        const uint32_t nstage_lo = nstage * kStageLo;
-        if (has_next) { B200FA_WAIT(&q_full[nstage], nphase, 0x711); }
-        // dV += P^T dO, then S^T of the next step (it overwrites P^T, in issue order)
-        B200FA_WAIT(p_full, i & 1, 0x710);
+      if (warp == 8) {
+        B200FA_WAIT(kv_full, 0, 0x700);
+        B200FA_WAIT(&q_full[0], 0, 0x701);
         tc_fence_after();
-        TRACE(3, 21);
-        issue_ts(tDV, tS, mDO, stage_lo, i == 0);
-        if (has_next) {
-          issue_kmajor(tS, kK, kQ, nstage_lo);
-          umma_commit(s_full);
+        issue_kmajor(tS, kK, kQ, 0);
+        umma_commit(s_full);
+        for (int i = 0; i < steps; ++i) {
+          const int stage = i % Cfg::kStages;
+          const uint32_t stage_lo = stage * kStageLo;
+          if (i + 1 < steps) {
+            // S^T of the next step as soon as this step's S^T sits in registers
+            const int nstage = (i + 1) % Cfg::kStages;
+            B200FA_WAIT(&q_full[nstage], static_cast<uint32_t>(((i + 1) / Cfg::kStages) & 1), 0x711);
+            B200FA_WAIT(s_free, i & 1, 0x714);
+            tc_fence_after();
+            issue_kmajor(tS, kK, kQ, nstage * kStageLo);
+            umma_commit(s_full);
+          }
+          // dV += P^T dO   (A = P^T tile in shared memory, K-major over the query index)
+          B200FA_WAIT(&do_full[stage], static_cast<uint32_t>((i / Cfg::kStages) & 1), 0x715);
+          B200FA_WAIT(p_full, i & 1, 0x710);
+          tc_fence_after();
+          TRACE(3, 21);
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t a_off = umma_off((kk >> 2) * kSubTileBytes + (kk & 3) * 32);
+            const uint32_t b_lo = mDO.lo + stage_lo + umma_off(kk * 2048);
+            if (kk == 0 && i == 0) umma_ss_fast<false>(tDV, kP.lo + a_off, kP.hi, b_lo, mDO.hi, idesc_acc);
+            else                   umma_ss_fast<true>(tDV, kP.lo + a_off, kP.hi, b_lo, mDO.hi, idesc_acc);
+          }
+          umma_commit(p_empty);
+          umma_commit(&qdo_empty[stage]);   // this lane is done with Q_i (S^T) and dO_i (dV)
         }
-        if (has_next) { B200FA_WAIT(&do_full[nstage], nphase, 0x713); }
-        // dK += dS^T Q, then dP^T of the next step (it overwrites dS^T, in issue order)
-        B200FA_WAIT(ds_full, i & 1, 0x712);
+        umma_commit(acc_full);
+      } else {
+        B200FA_WAIT(kv_full, 0, 0x720);
+        B200FA_WAIT(&do_full[0], 0, 0x702);
         tc_fence_after();
-        TRACE(3, 23);
-        issue_ts(tDK, tDP, mQ, stage_lo, i == 0);
-        umma_commit(&qdo_empty[stage]);
-        if (has_next) {
-          issue_kmajor(tDP, kV, kDO, nstage_lo);
-          umma_commit(dp_full);
+        issue_kmajor(tDP, kV, kDO, 0);
+        umma_commit(dp_full);
+        for (int i = 0; i < steps; ++i) {
+          const int stage = i % Cfg::kStages;
+          const uint32_t stage_lo = stage * kStageLo;
+          // dK += dS^T Q   (A = 16-bit dS^T in the dP^T columns)
+          B200FA_WAIT(&q_full[stage], static_cast<uint32_t>((i / Cfg::kStages) & 1), 0x716);
+          B200FA_WAIT(ds_full, i & 1, 0x712);
+          tc_fence_after();
+          TRACE(4, 23);
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t a_col = (kk < 4) ? kk * 8 : 64 + (kk - 4) * 8;
+            const uint32_t b_lo = mQ.lo + stage_lo + umma_off(kk * 2048);
+            if (kk == 0 && i == 0) umma_ts_fast<false>(tDK, tDP + a_col, b_lo, mQ.hi, idesc_acc);
+            else                   umma_ts_fast<true>(tDK, tDP + a_col, b_lo, mQ.hi, idesc_acc);
+          }
+          umma_commit(&qdo_empty[stage]);   // this lane is done with Q_i (dK) and dO_i (dP^T)
+          if (i + 1 < steps) {
+            // dP^T of the next step overwrites dS^T, in issue order behind dK
+            const int nstage = (i + 1) % Cfg::kStages;
+            B200FA_WAIT(&do_full[nstage], static_cast<uint32_t>(((i + 1) / Cfg::kStages) & 1), 0x713);
+            tc_fence_after();
+            issue_kmajor(tDP, kV, kDO, nstage * kStageLo);
+            umma_commit(dp_full);
+          }
         }
+        umma_commit(acc_full);
       }
-      umma_commit(acc_full);
     }
-  } else if (warp == 9) {
+  } else if (warp == 10) {
     // =========================== TMA producer ===========================
     if (lane == 0) {
       auto load_tile = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int srow, int head) {
@@ -453,7 +494,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
-  if (warp == 9 && lane == 0) {
+  if (warp == 10 && lane == 0) {
     tma_prefetch_desc(&mapQ);
     tma_prefetch_desc(&mapK);
     tma_prefetch_desc(&mapV);
@@ -539,8 +580,11 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
         if (valid) store_row_16bit<kBf16>(dst + ch * 32, reinterpret_cast<const float*>(a), p.scale);
       }
     }
-  } else if (warp == 8) {
-    // =========================== MMA issuer ===========================
+  } else if (warp == 8 || warp == 9) {
+    // =========================== MMA issuers ===========================
+    // Warp 8: dQ += dS_j K_j, then S of tile j+2 into the buffer dS_j just left.
+    // Warp 9: dP of tile j+1.  Separate lanes so that neither chain stalls behind the other's
+    // operands (an issuing lane is blocked while the tensor pipe is full).
     if (lane == 0) {
       constexpr uint32_t idesc_s = umma_idesc(kBf16, false, false, 128, 128);   // S, dP
       constexpr uint32_t idesc_dq = umma_idesc(kBf16, false, true, 128, kD);    // dQ (A from TMEM, K MN-major)
@@ -557,61 +601,68 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
         }
       };
       constexpr uint32_t kTileLo = umma_off(Cfg::kTileBytes);
-      // prologue: S_0, dP_0, S_1
-      B200FA_WAIT(qdo_full, 0, 0xa00);
-      B200FA_WAIT(&k_full[0], 0, 0xa01);
-      tc_fence_after();
-      issue_kmajor(tmem_base + kTmemS, kQ, kK, 0);
-      umma_commit(&s_full[0]);
-      B200FA_WAIT(&v_full[0], 0, 0xa03);
-      tc_fence_after();
-      issue_kmajor(tDP, kDO, kV, 0);
-      umma_commit(dp_full);
-      umma_commit(&v_empty[0]);
-      if (n_tiles > 1) {
-        B200FA_WAIT(&k_full[1], 0, 0xa02);
+      if (warp == 8) {
+        // prologue: S_0, S_1
+        B200FA_WAIT(qdo_full, 0, 0xa00);
+        B200FA_WAIT(&k_full[0], 0, 0xa01);
         tc_fence_after();
-        issue_kmajor(tmem_base + kTmemS + 128, kQ, kK, kTileLo);
-        umma_commit(&s_full[1]);
-      }
-      int kslot = 0;  // ring slot of K_j
-      for (int j = 0; j < n_tiles; ++j) {
-        const int buf = j & 1;
-        const uint32_t tSj = tmem_base + kTmemS + buf * 128;
-        const int k2slot = (kslot == 0) ? 2 : kslot - 1;   // slot of K_{j+2} = (j + 2) % 3
-        if (j + 1 < n_tiles) { B200FA_WAIT(&v_full[buf ^ 1], ((j + 1) >> 1) & 1, 0xa12); }
-        // compute has read dP_j and written dS_j over S_j
-        B200FA_WAIT(ds_full, j & 1, 0xa10);
-        tc_fence_after();
-        TRACE(3, 21);
-        if (j + 1 < n_tiles) {
-          // dP of the next tile first, so the compute warps get it while dQ runs
-          issue_kmajor(tDP, kDO, kV, (buf ^ 1) * kTileLo);
-          umma_commit(dp_full);
-          umma_commit(&v_empty[buf ^ 1]);
-        }
-        // dQ += dS_j K_j   (A = 16-bit dS in the S_j columns, B = K_j rows as the contraction index)
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t a_col = (kk < 4) ? kk * 8 : 64 + (kk - 4) * 8;
-          const uint32_t b_lo = mK.lo + kslot * kTileLo + umma_off(kk * 2048);
-          if (kk == 0 && j == 0) umma_ts_fast<false>(tDQ, tSj + a_col, b_lo, mK.hi, idesc_dq);
-          else                   umma_ts_fast<true>(tDQ, tSj + a_col, b_lo, mK.hi, idesc_dq);
-        }
-        umma_commit(&k_empty[kslot]);
-        if (j + 2 < n_tiles) {
-          // S of tile j+2 re-uses this S buffer
-          B200FA_WAIT(&k_full[k2slot], static_cast<uint32_t>(((j + 2) / 3) & 1), 0xa11);
+        issue_kmajor(tmem_base + kTmemS, kQ, kK, 0);
+        umma_commit(&s_full[0]);
+        if (n_tiles > 1) {
+          B200FA_WAIT(&k_full[1], 0, 0xa02);
           tc_fence_after();
-          TRACE(3, 22);
-          issue_kmajor(tSj, kQ, kK, k2slot * kTileLo);
-          umma_commit(&s_full[buf]);
+          issue_kmajor(tmem_base + kTmemS + 128, kQ, kK, kTileLo);
+          umma_commit(&s_full[1]);
         }
-        if (++kslot == 3) kslot = 0;
+        int kslot = 0;  // ring slot of K_j
+        for (int j = 0; j < n_tiles; ++j) {
+          const int buf = j & 1;
+          const uint32_t tSj = tmem_base + kTmemS + buf * 128;
+          const int k2slot = (kslot == 0) ? 2 : kslot - 1;   // slot of K_{j+2} = (j + 2) % 3
+          // compute has written dS_j over S_j
+          B200FA_WAIT(ds_full, j & 1, 0xa10);
+          tc_fence_after();
+          TRACE(3, 21);
+          // dQ += dS_j K_j   (A = 16-bit dS in the S_j columns, B = K_j rows as the contraction index)
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t a_col = (kk < 4) ? kk * 8 : 64 + (kk - 4) * 8;
+            const uint32_t b_lo = mK.lo + kslot * kTileLo + umma_off(kk * 2048);
+            if (kk == 0 && j == 0) umma_ts_fast<false>(tDQ, tSj + a_col, b_lo, mK.hi, idesc_dq);
+            else                   umma_ts_fast<true>(tDQ, tSj + a_col, b_lo, mK.hi, idesc_dq);
+          }
+          umma_commit(&k_empty[kslot]);
+          if (j + 2 < n_tiles) {
+            // S of tile j+2 re-uses this S buffer
+            B200FA_WAIT(&k_full[k2slot], static_cast<uint32_t>(((j + 2) / 3) & 1), 0xa11);
+            tc_fence_after();
+            TRACE(3, 22);
+            issue_kmajor(tSj, kQ, kK, k2slot * kTileLo);
+            umma_commit(&s_full[buf]);
+          }
+          if (++kslot == 3) kslot = 0;
+        }
+        umma_commit(acc_full);
+      } else {
+        // dP_0, then dP_{j+1} whenever the compute warps have consumed dP_j
+        B200FA_WAIT(qdo_full, 0, 0xa20);
+        B200FA_WAIT(&v_full[0], 0, 0xa03);
+        tc_fence_after();
+        issue_kmajor(tDP, kDO, kV, 0);
+        umma_commit(dp_full);
+        umma_commit(&v_empty[0]);
+        for (int j = 0; j + 1 < n_tiles; ++j) {
+          const int vslot = (j + 1) & 1;
+          B200FA_WAIT(&v_full[vslot], ((j + 1) >> 1) & 1, 0xa12);
+          B200FA_WAIT(ds_full, j & 1, 0xa13);
+          tc_fence_after();
+          issue_kmajor(tDP, kDO, kV, vslot * kTileLo);
+          umma_commit(dp_full);
+          umma_commit(&v_empty[vslot]);
+        }
       }
-      umma_commit(acc_full);
     }
-  } else if (warp == 9) {
+  } else if (warp == 10) {
     // =========================== TMA producer ===========================
     if (lane == 0) {
       auto load_tile = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int srow, int head) {

@@ -13,7 +13,7 @@ aggregate over all ranks.  FLOPs follow the reference's convention: forward
 Rank 0 prints ONE JSON line.  ``value`` is timed with CUDA events on tensors already resident
 in HBM; ``e2e`` runs the same step through the public `mojo`-device operator API with pinned
 HOST buffers, host<->device copies inside the timed region; ``roofline`` times the dominant
-kernel (the dK/dV/dQ backward kernel) alone; ``cpu_baseline`` is the CPU oracle timed on the
+kernel (the backward dK/dV kernel) alone; ``cpu_baseline`` is the CPU oracle timed on the
 host cores on a bounded slice of the same workload.
 """
 
@@ -36,9 +36,9 @@ sys.path.insert(0, ROOT)
 METRIC = "flash-attn fwd+bwd TFLOP/s (bf16, causal)"
 NOMINAL_BF16_TFLOPS = 2250.0
 FALLBACK_BF16_TFLOPS = 1590.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the backward main kernel on the
-# bench workload, from the ncu capture summarised in profiles/ (None until captured).
-BWD_MAIN_DRAM_TRAFFIC_BYTES = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the backward dK/dV kernel on the
+# C3 workload, from the ncu capture summarised in profiles/bwd_dkdv_kernel_C3.md.
+BWD_DKDV_DRAM_TRAFFIC_BYTES = 397.5e6
 
 
 def load_peaks():
@@ -205,23 +205,24 @@ def run_ours(args):
         e1.record()
         barrier(world)
         total_ms = max_over_ranks(e0.elapsed_time(e1), world)
-        # forward-only and main-backward-kernel-only timings explain the step number
+        # forward-only and single-backward-kernel timings explain the step number
         ef0.record()
         for _ in range(args.steps):
             raw.flash_fwd(q, k, v, causal=cfg.causal, scale=cfg.scale, out=out, lse=lse, status=status)
         ef1.record()
         torch.cuda.synchronize()
         fwd_ms = ef0.elapsed_time(ef1) / args.steps
-        bwd_main_ms = None
+        bwd_part_ms = {}
         if do_bwd:
-            eb0, eb1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            eb0.record()
-            for _ in range(args.steps):
-                raw.flash_bwd(dout, q, k, v, out, lse, causal=cfg.causal, scale=cfg.scale, dq=dq, dk=dk, dv=dv,
-                              workspace=ws, status=status, parts=2)
-            eb1.record()
-            torch.cuda.synchronize()
-            bwd_main_ms = eb0.elapsed_time(eb1) / args.steps
+            for name, part in (("dkdv", 2), ("dq", 4)):
+                eb0, eb1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                eb0.record()
+                for _ in range(args.steps):
+                    raw.flash_bwd(dout, q, k, v, out, lse, causal=cfg.causal, scale=cfg.scale, dq=dq, dk=dk, dv=dv,
+                                  workspace=ws, status=status, parts=part)
+                eb1.record()
+                torch.cuda.synchronize()
+                bwd_part_ms[name] = eb0.elapsed_time(eb1) / args.steps
     launches = (_lib.launch_count() - launches0)
     timed_launches = args.steps * (1 + (3 if do_bwd else 0))
     if int(status.item()) != 0:
@@ -236,7 +237,9 @@ def run_ours(args):
 
     burst, sustained, peak_src = load_peaks()
     if do_bwd:
-        dom_flops, dom_ms, dom_name = cfg.bwd_flops(), bwd_main_ms, "bwd_kernel (dK/dV/dQ tcgen05 pipeline)"
+        # The dK/dV kernel is the longest launch.  Its algorithmic work is the 4 tile GEMMs of the 5 a
+        # backward needs that it covers (S^T, dP^T, dV, dK): 0.8 x the backward FLOPs (2.0 x forward).
+        dom_flops, dom_ms, dom_name = 0.8 * cfg.bwd_flops(), bwd_part_ms["dkdv"], "bwd_dkdv_kernel (S^T, dP^T, dV, dK)"
     else:
         dom_flops, dom_ms, dom_name = cfg.fwd_flops(), fwd_ms, "fwd_kernel"
     achieved = dom_flops / (dom_ms * 1e-3) / 1e12
@@ -244,7 +247,7 @@ def run_ours(args):
         "bound": "tensor", "kernel": dom_name, "achieved": round(achieved, 2), "peak": burst, "unit": "TFLOP/s",
         "frac": round(achieved / burst, 4), "peak_source": f"of {peak_src} (cuBLAS bf16 burst)",
         "frac_of_nominal_2250": round(achieved / NOMINAL_BF16_TFLOPS, 4),
-        "traffic": BWD_MAIN_DRAM_TRAFFIC_BYTES if do_bwd else None,
+        "traffic": BWD_DKDV_DRAM_TRAFFIC_BYTES if (do_bwd and cfg.name == "C3") else None,
         "ms_per_launch": round(dom_ms, 4),
     }
     detail = {
@@ -256,7 +259,7 @@ def run_ours(args):
         detail.update({
             "bwd_ms": round(bwd_ms, 4), "bwd_tflops": round(cfg.bwd_flops() / (bwd_ms * 1e-3) / 1e12, 2),
             "bwd_frac_of_nominal_2250": round(cfg.bwd_flops() / (bwd_ms * 1e-3) / 1e12 / NOMINAL_BF16_TFLOPS, 4),
-            "bwd_main_kernel_ms": round(bwd_main_ms, 4),
+            "bwd_dkdv_kernel_ms": round(bwd_part_ms["dkdv"], 4), "bwd_dq_kernel_ms": round(bwd_part_ms["dq"], 4),
         })
 
     cpu_baseline = None

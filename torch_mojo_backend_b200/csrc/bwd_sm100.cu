@@ -20,7 +20,7 @@
 //
 // Both kernels: warps 0-3 and 4-7 are two compute warpgroups that split the 128 score
 // columns of a tile in halves (thread <-> TMEM lane), warps 8 and 9 each issue one of the two
-// independent MMA chains, warp 10 drives TMA, warp 11 idles.
+// independent MMA chains (the dK/dV kernel uses warp 10 for a third), the next warp drives TMA.
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -155,7 +155,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
-  if (warp == 10 && lane == 0) {
+  if (warp == 11 && lane == 0) {
     tma_prefetch_desc(&mapQ);
     tma_prefetch_desc(&mapK);
     tma_prefetch_desc(&mapV);
@@ -281,12 +281,15 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         }
       }
     }
-  } else if (warp == 8 || warp == 9) {
+  } else if (warp >= 8 && warp <= 10) {
     // =========================== MMA issuers ===========================
     // A tcgen05.mma only issues once the tensor pipe has room, so an issuing lane is stalled
-    // for about as long as its MMAs run.  The S^T -> P^T -> dV chain and the dP^T -> dS^T -> dK
-    // chain are independent, so each gets its own lane: neither waits behind the other's
-    // operands.  Warp 8: S^T of the next step and dV.  Warp 9: dK and dP^T of the next step.
+    // for about as long as its MMAs run, and it handles its waits strictly in program order.
+    // The three dependency chains of a step therefore get a lane each, so none of them waits
+    // behind another chain's operands:
+    //   warp 8:  S^T of the next step      (needs the next Q tile and S^T of this step in registers)
+    //   warp 9:  dK, then dP^T of the next step   (needs dS^T, the next dO tile)
+    //   warp 10: dV                        (needs P^T in shared memory); frees the Q/dO stage
     if (lane == 0) {
       constexpr uint32_t idesc_st = umma_idesc(kBf16, false, false, 128, 128);  // S^T, dP^T
       constexpr uint32_t idesc_acc = umma_idesc(kBf16, false, true, 128, kD);   // dV (A in smem), dK (A in TMEM)
@@ -313,39 +316,19 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
       constexpr uint32_t kStageLo = umma_off(2 * Cfg::kTileBytes);
       if (warp == 8) {
         B200FA_WAIT(kv_full, 0, 0x700);
-        B200FA_WAIT(&q_full[0], 0, 0x701);
-        tc_fence_after();
-        issue_kmajor(tS, kK, kQ, 0);
-        umma_commit(s_full);
         for (int i = 0; i < steps; ++i) {
           const int stage = i % Cfg::kStages;
-          const uint32_t stage_lo = stage * kStageLo;
-          if (i + 1 < steps) {
-            // S^T of the next step as soon as this step's S^T sits in registers
-            const int nstage = (i + 1) % Cfg::kStages;
-            B200FA_WAIT(&q_full[nstage], static_cast<uint32_t>(((i + 1) / Cfg::kStages) & 1), 0x711);
-            B200FA_WAIT(s_free, i & 1, 0x714);
-            tc_fence_after();
-            issue_kmajor(tS, kK, kQ, nstage * kStageLo);
-            umma_commit(s_full);
-          }
-          // dV += P^T dO   (A = P^T tile in shared memory, K-major over the query index)
-          B200FA_WAIT(&do_full[stage], static_cast<uint32_t>((i / Cfg::kStages) & 1), 0x715);
-          B200FA_WAIT(p_full, i & 1, 0x710);
+          B200FA_WAIT(&q_full[stage], static_cast<uint32_t>((i / Cfg::kStages) & 1), 0x711);
+          TRACE(3, 26);
+          // the compute warps must hold S^T of the previous step in registers
+          if (i > 0) { B200FA_WAIT(s_free, (i - 1) & 1, 0x714); }
           tc_fence_after();
-          TRACE(3, 21);
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
-            const uint32_t a_off = umma_off((kk >> 2) * kSubTileBytes + (kk & 3) * 32);
-            const uint32_t b_lo = mDO.lo + stage_lo + umma_off(kk * 2048);
-            if (kk == 0 && i == 0) umma_ss_fast<false>(tDV, kP.lo + a_off, kP.hi, b_lo, mDO.hi, idesc_acc);
-            else                   umma_ss_fast<true>(tDV, kP.lo + a_off, kP.hi, b_lo, mDO.hi, idesc_acc);
-          }
-          umma_commit(p_empty);
-          umma_commit(&qdo_empty[stage]);   // this lane is done with Q_i (S^T) and dO_i (dV)
+          TRACE(3, 24);
+          issue_kmajor(tS, kK, kQ, stage * kStageLo);
+          umma_commit(s_full);
+          TRACE(3, 25);
         }
-        umma_commit(acc_full);
-      } else {
+      } else if (warp == 9) {
         B200FA_WAIT(kv_full, 0, 0x720);
         B200FA_WAIT(&do_full[0], 0, 0x702);
         tc_fence_after();
@@ -367,6 +350,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             else                   umma_ts_fast<true>(tDK, tDP + a_col, b_lo, mQ.hi, idesc_acc);
           }
           umma_commit(&qdo_empty[stage]);   // this lane is done with Q_i (dK) and dO_i (dP^T)
+          TRACE(4, 28);
           if (i + 1 < steps) {
             // dP^T of the next step overwrites dS^T, in issue order behind dK
             const int nstage = (i + 1) % Cfg::kStages;
@@ -377,9 +361,30 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
           }
         }
         umma_commit(acc_full);
+      } else {
+        for (int i = 0; i < steps; ++i) {
+          const int stage = i % Cfg::kStages;
+          const uint32_t stage_lo = stage * kStageLo;
+          // dV += P^T dO   (A = P^T tile in shared memory, K-major over the query index)
+          B200FA_WAIT(&do_full[stage], static_cast<uint32_t>((i / Cfg::kStages) & 1), 0x715);
+          B200FA_WAIT(p_full, i & 1, 0x710);
+          tc_fence_after();
+          TRACE(5, 21);
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint32_t a_off = umma_off((kk >> 2) * kSubTileBytes + (kk & 3) * 32);
+            const uint32_t b_lo = mDO.lo + stage_lo + umma_off(kk * 2048);
+            if (kk == 0 && i == 0) umma_ss_fast<false>(tDV, kP.lo + a_off, kP.hi, b_lo, mDO.hi, idesc_acc);
+            else                   umma_ss_fast<true>(tDV, kP.lo + a_off, kP.hi, b_lo, mDO.hi, idesc_acc);
+          }
+          umma_commit(p_empty);
+          umma_commit(&qdo_empty[stage]);   // this lane is done with dO_i; S^T of Q_i completed long ago
+          TRACE(5, 27);
+        }
+        umma_commit(acc_full);
       }
     }
-  } else if (warp == 10) {
+  } else if (warp == 11) {
     // =========================== TMA producer ===========================
     if (lane == 0) {
       auto load_tile = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int srow, int head) {
@@ -397,6 +402,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         if (i >= Cfg::kStages) {
           B200FA_WAIT(&qdo_empty[stage], ((i / Cfg::kStages) - 1) & 1, 0x800);
         }
+        TRACE(6, 30);
         const int64_t stat_off = (static_cast<int64_t>(b) * p.Hq + h) * p.Spad + m_tile * kTile;
         float* st = sStat + stage * 256;
         uint8_t* q_dst = sQ + stage * 2 * Cfg::kTileBytes;

@@ -41,7 +41,8 @@ namespace b200fa {
 namespace {
 
 constexpr int kTile = 128;
-constexpr int kThreads = 384;
+constexpr int kThreads = 384;        // dQ kernel: 8 compute warps + 4
+constexpr int kDkdvThreads = 640;    // dK/dV kernel: 16 compute warps + 4
 constexpr int kSubTileBytes = 128 * 128;
 
 template <int kD>
@@ -75,6 +76,19 @@ __device__ __forceinline__ void store_row_16bit(uint16_t* dst, const float* v, f
   }
 }
 
+template <bool kBf16>
+__device__ __forceinline__ void store_half_row_16bit(uint16_t* dst, const float* v, float mul) {
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    uint4 w;
+    w.x = pack2<kBf16>(v[g * 8 + 0] * mul, v[g * 8 + 1] * mul);
+    w.y = pack2<kBf16>(v[g * 8 + 2] * mul, v[g * 8 + 3] * mul);
+    w.z = pack2<kBf16>(v[g * 8 + 4] * mul, v[g * 8 + 5] * mul);
+    w.w = pack2<kBf16>(v[g * 8 + 6] * mul, v[g * 8 + 7] * mul);
+    *reinterpret_cast<uint4*>(dst + g * 8) = w;
+  }
+}
+
 #define B200FA_WAIT(bar, parity, site) \
   if (!mbar_wait((bar), (parity), abort_flag, p.status, (site))) goto teardown
 
@@ -86,12 +100,14 @@ __device__ __forceinline__ void store_row_16bit(uint16_t* dst, const float* v, f
 // S^T of the next step can be issued while the exponentials of this step are still running.
 // ------------------------------------------------------------------------------------------
 template <int kD, bool kBf16, bool kCausal>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kDkdvThreads, 1)
 bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                 const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
                 const BwdParams p) {
   using Cfg = BwdCfg<kD>;
-  constexpr int kTmemS = 0, kTmemDP = 128, kTmemDV = 256, kTmemDK = 256 + kD;
+  // TMEM: two 128-column work buffers (step i uses buffer i & 1 for S^T, then dP^T, then dS^T),
+  // then the dV and dK accumulators.
+  constexpr int kTmemWork = 0, kTmemDV = 256, kTmemDK = 256 + kD;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* sK = smem + Cfg::kOffResident;
   uint8_t* sV = sK + Cfg::kTileBytes;
@@ -103,8 +119,9 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   uint64_t* q_full = kv_full + 1;                  // [kStages]  Q tile + lse2
   uint64_t* do_full = q_full + Cfg::kStages;       // [kStages]  dO tile + dpsum
   uint64_t* qdo_empty = do_full + Cfg::kStages;    // [kStages]
-  uint64_t* s_full = qdo_empty + Cfg::kStages;     // S^T ready
-  uint64_t* dp_full = s_full + 1;                  // dP^T ready
+  uint64_t* s_full = qdo_empty + Cfg::kStages;     // [2]  S^T ready in work buffer b
+  uint64_t* buf_free = s_full + 2;                 // [2]  dK MMA has consumed dS^T from work buffer b
+  uint64_t* dp_full = buf_free + 2;                // dP^T ready
   uint64_t* p_full = dp_full + 1;                  // P^T written  (8 warp arrivals)
   uint64_t* ds_full = p_full + 1;                  // dS^T written (8 warp arrivals)
   uint64_t* acc_full = ds_full + 1;                // dK, dV complete
@@ -140,22 +157,25 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
       mbar_init(&do_full[i], 1);
       mbar_init(&qdo_empty[i], 2);   // both MMA-issuing lanes release a stage
     }
-    mbar_init(s_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&buf_free[i], 1);
+    }
     mbar_init(dp_full, 1);
-    mbar_init(p_full, 8);   // one elected arrival per compute warp
-    mbar_init(ds_full, 8);
+    mbar_init(p_full, 16);   // one elected arrival per compute warp
+    mbar_init(ds_full, 16);
     mbar_init(acc_full, 2);        // both MMA-issuing lanes
-    mbar_init(s_free, 8);
+    mbar_init(s_free, 16);
     mbar_init(p_empty, 1);
     *abort_flag = 0;
     fence_mbar_init();
     fence_proxy_async_smem();
   }
-  if (warp == 8) {
+  if (warp == 16) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
-  if (warp == 11 && lane == 0) {
+  if (warp == 19 && lane == 0) {
     tma_prefetch_desc(&mapQ);
     tma_prefetch_desc(&mapK);
     tma_prefetch_desc(&mapV);
@@ -166,41 +186,41 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp < 8) {
+  if (warp < 16) {
     // =========================== compute warps ===========================
-    const int wg = warp >> 2;                       // which 64-column (query) half of the tile
+    const int wg = warp >> 2;                       // which 32-column (query) quarter of the tile
     const int j = (warp & 3) * 32 + lane;           // key row inside the tile == TMEM lane
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t tS = tmem_base + lane_off + kTmemS + wg * 64;
-    const uint32_t tDP = tmem_base + lane_off + kTmemDP + wg * 64;
+    const uint32_t tWork = tmem_base + lane_off + kTmemWork + wg * 32;
     const float c = p.scale_log2;
-    // this thread's 128-byte row of the 128-byte-swizzled P^T tile (64 query columns)
-    uint8_t* p_row = sP + wg * kSubTileBytes + j * 128;
+    // this thread's 64 bytes (32 query columns) of its row of the 128-byte-swizzled P^T tile
+    uint8_t* p_row = sP + (wg >> 1) * kSubTileBytes + j * 128;
+    const int chunk0 = (wg & 1) * 4;
     for (int i = 0; i < steps; ++i) {
       const int stage = i % Cfg::kStages;
       const uint32_t ring_phase = static_cast<uint32_t>((i / Cfg::kStages) & 1);
       const int m_tile = m_start + i % per_head;
-      const float4* lse2 = reinterpret_cast<const float4*>(sStat + stage * 256 + wg * 64);
+      const float4* lse2 = reinterpret_cast<const float4*>(sStat + stage * 256 + wg * 32);
       const float4* dps = lse2 + 32;
       // ---- P^T = exp2(S^T * c - lse2).  S^T is pulled into registers in one go and released
-      // at once, so the MMA warp can start S^T of the next step while the exponentials run;
+      // at once, so the S^T MMA of the next step can run while the exponentials do;
       // P^T goes to shared memory (the A operand of dV += P^T dO) instead of back over S^T.
-      B200FA_WAIT(s_full, i & 1, 0x500);
+      // S^T, dP^T and dS^T of this step live one after the other in work buffer i & 1
+      const uint32_t tS = tWork + (i & 1) * 128, tDP = tS;
+      B200FA_WAIT(&s_full[i & 1], (i >> 1) & 1, 0x500);
       // lse2 rode in with the Q tile; observing its barrier directly makes the bulk copy visible here
       B200FA_WAIT(&q_full[stage], ring_phase, 0x501);
       tc_fence_after();
-      if ((warp & 3) == 0) TRACE(wg, 1);
-      float pf[64];
+      if ((warp & 3) == 0) TRACE(wg & 1, 1);
+      float pf[32];
       {
-        uint32_t* s = reinterpret_cast<uint32_t*>(pf);
-        tmem_ld32(tS, s);
-        tmem_ld32(tS + 32, s + 32);
+        tmem_ld32(tS, reinterpret_cast<uint32_t*>(pf));
         tmem_wait_ld();
         tc_fence_before();
         mbar_arrive_warp(s_free);
       }
 #pragma unroll
-      for (int e4 = 0; e4 < 16; ++e4) {
+      for (int e4 = 0; e4 < 8; ++e4) {
         const float4 l4 = lse2[e4];
         pf[e4 * 4 + 0] = ex2_approx(fmaf(pf[e4 * 4 + 0], c, -l4.x));
         pf[e4 * 4 + 1] = ex2_approx(fmaf(pf[e4 * 4 + 1], c, -l4.y));
@@ -210,60 +230,59 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
       if (kCausal && m_tile == n_tile) {
         // on the diagonal tile, query column q sees key row j only if j <= q
 #pragma unroll
-        for (int e = 0; e < 64; ++e) {
-          if (j > wg * 64 + e) pf[e] = 0.f;
+        for (int e = 0; e < 32; ++e) {
+          if (j > wg * 32 + e) pf[e] = 0.f;
         }
       }
       // the previous step's dV MMA must have finished reading the P^T tile
       if (i > 0) { B200FA_WAIT(p_empty, (i - 1) & 1, 0x502); }
 #pragma unroll
-      for (int chunk = 0; chunk < 8; ++chunk) {
+      for (int chunk = 0; chunk < 4; ++chunk) {
         uint4 w;
         w.x = pack2<kBf16>(pf[chunk * 8 + 0], pf[chunk * 8 + 1]);
         w.y = pack2<kBf16>(pf[chunk * 8 + 2], pf[chunk * 8 + 3]);
         w.z = pack2<kBf16>(pf[chunk * 8 + 4], pf[chunk * 8 + 5]);
         w.w = pack2<kBf16>(pf[chunk * 8 + 6], pf[chunk * 8 + 7]);
-        *reinterpret_cast<uint4*>(p_row + ((chunk ^ (j & 7)) << 4)) = w;
+        *reinterpret_cast<uint4*>(p_row + (((chunk0 + chunk) ^ (j & 7)) << 4)) = w;
       }
       fence_proxy_async_smem();
       mbar_arrive_warp(p_full);
-      if ((warp & 3) == 0) TRACE(wg, 2);
+      if ((warp & 3) == 0) TRACE(wg & 1, 2);
       // ---- dS^T = P^T * (dP^T - dpsum)
       B200FA_WAIT(dp_full, i & 1, 0x510);
       B200FA_WAIT(&do_full[stage], ring_phase, 0x511);
       tc_fence_after();
-      if ((warp & 3) == 0) TRACE(wg, 3);
-#pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
+      if ((warp & 3) == 0) TRACE(wg & 1, 3);
+      {
         uint32_t d[32];
-        tmem_ld32(tDP + ch * 32, d);
+        tmem_ld32(tDP, d);
         tmem_wait_ld();
         const float* df = reinterpret_cast<const float*>(d);
         uint32_t pk[16];
 #pragma unroll
         for (int e4 = 0; e4 < 8; ++e4) {
-          const float4 d4 = dps[ch * 8 + e4];
-          const float a0 = pf[ch * 32 + e4 * 4 + 0] * (df[e4 * 4 + 0] - d4.x);
-          const float a1 = pf[ch * 32 + e4 * 4 + 1] * (df[e4 * 4 + 1] - d4.y);
-          const float a2 = pf[ch * 32 + e4 * 4 + 2] * (df[e4 * 4 + 2] - d4.z);
-          const float a3 = pf[ch * 32 + e4 * 4 + 3] * (df[e4 * 4 + 3] - d4.w);
+          const float4 d4 = dps[e4];
+          const float a0 = pf[e4 * 4 + 0] * (df[e4 * 4 + 0] - d4.x);
+          const float a1 = pf[e4 * 4 + 1] * (df[e4 * 4 + 1] - d4.y);
+          const float a2 = pf[e4 * 4 + 2] * (df[e4 * 4 + 2] - d4.z);
+          const float a3 = pf[e4 * 4 + 3] * (df[e4 * 4 + 3] - d4.w);
           pk[e4 * 2] = pack2<kBf16>(a0, a1);
           pk[e4 * 2 + 1] = pack2<kBf16>(a2, a3);
         }
-        tmem_st16(tDP + ch * 16, pk);
+        tmem_st16(tDP, pk);
       }
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive_warp(ds_full);
-      if ((warp & 3) == 0) TRACE(wg, 4);
+      if ((warp & 3) == 0) TRACE(wg & 1, 4);
     }
-    // ---- epilogue: dV and dK (this warpgroup's half of the head dimension)
+    // ---- epilogue: dV and dK (this warpgroup's quarter of the head dimension)
     B200FA_WAIT(acc_full, 0, 0x520);
     tc_fence_after();
     {
       const int krow = n0 + j;
       const bool valid = krow < p.S;
-      constexpr int kHalf = kD / 2;
+      constexpr int kHalf = kD / 4;
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         const View4& dst_view = which == 0 ? p.dv : p.dk;
@@ -272,29 +291,32 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                          static_cast<int64_t>(krow) * dst_view.ss) + wg * kHalf;
         const uint32_t tacc = tmem_base + lane_off + (which == 0 ? kTmemDV : kTmemDK) + wg * kHalf;
         const float mul = which == 0 ? 1.f : p.scale;
-#pragma unroll
-        for (int ch = 0; ch < kHalf / 32; ++ch) {
+        if constexpr (kHalf == 32) {
           uint32_t a[32];
-          tmem_ld32(tacc + ch * 32, a);
+          tmem_ld32(tacc, a);
           tmem_wait_ld();
-          if (valid) store_row_16bit<kBf16>(dst + ch * 32, reinterpret_cast<const float*>(a), mul);
+          if (valid) store_row_16bit<kBf16>(dst, reinterpret_cast<const float*>(a), mul);
+        } else {
+          uint32_t a[16];
+          tmem_ld16(tacc, a);
+          tmem_wait_ld();
+          if (valid) store_half_row_16bit<kBf16>(dst, reinterpret_cast<const float*>(a), mul);
         }
       }
     }
-  } else if (warp >= 8 && warp <= 10) {
+  } else if (warp >= 16 && warp <= 18) {
     // =========================== MMA issuers ===========================
     // A tcgen05.mma only issues once the tensor pipe has room, so an issuing lane is stalled
     // for about as long as its MMAs run, and it handles its waits strictly in program order.
     // The three dependency chains of a step therefore get a lane each, so none of them waits
     // behind another chain's operands:
-    //   warp 8:  S^T of the next step      (needs the next Q tile and S^T of this step in registers)
-    //   warp 9:  dK, then dP^T of the next step   (needs dS^T, the next dO tile)
-    //   warp 10: dV                        (needs P^T in shared memory); frees the Q/dO stage
+    //   warp 16: S^T of the next step      (needs the next Q tile and S^T of this step in registers)
+    //   warp 17: dK, then dP^T of the next step   (needs dS^T, the next dO tile)
+    //   warp 18: dV                        (needs P^T in shared memory); frees the Q/dO stage
     if (lane == 0) {
       constexpr uint32_t idesc_st = umma_idesc(kBf16, false, false, 128, 128);  // S^T, dP^T
       constexpr uint32_t idesc_acc = umma_idesc(kBf16, false, true, 128, kD);   // dV (A in smem), dK (A in TMEM)
-      const uint32_t tS = tmem_base + kTmemS, tDP = tmem_base + kTmemDP, tDV = tmem_base + kTmemDV,
-                     tDK = tmem_base + kTmemDK;
+      const uint32_t tWork = tmem_base + kTmemWork, tDV = tmem_base + kTmemDV, tDK = tmem_base + kTmemDK;
       // Descriptors: fixed high word + start-address low word.  K-major form for the S^T / dP^T
       // operands and the P^T tile, MN-major form (LBO = next 64-column sub-tile) when Q / dO
       // are the B operand of an accumulating MMA.
@@ -314,49 +336,53 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         }
       };
       constexpr uint32_t kStageLo = umma_off(2 * Cfg::kTileBytes);
-      if (warp == 8) {
+      if (warp == 16) {
         B200FA_WAIT(kv_full, 0, 0x700);
         for (int i = 0; i < steps; ++i) {
           const int stage = i % Cfg::kStages;
           B200FA_WAIT(&q_full[stage], static_cast<uint32_t>((i / Cfg::kStages) & 1), 0x711);
           TRACE(3, 26);
-          // the compute warps must hold S^T of the previous step in registers
-          if (i > 0) { B200FA_WAIT(s_free, (i - 1) & 1, 0x714); }
+          // the dK MMA of step i - 2 must have consumed dS^T from this work buffer
+          if (i >= 2) { B200FA_WAIT(&buf_free[i & 1], ((i >> 1) - 1) & 1, 0x714); }
           tc_fence_after();
           TRACE(3, 24);
-          issue_kmajor(tS, kK, kQ, stage * kStageLo);
-          umma_commit(s_full);
+          issue_kmajor(tWork + (i & 1) * 128, kK, kQ, stage * kStageLo);
+          umma_commit(&s_full[i & 1]);
           TRACE(3, 25);
         }
-      } else if (warp == 9) {
+      } else if (warp == 17) {
         B200FA_WAIT(kv_full, 0, 0x720);
         B200FA_WAIT(&do_full[0], 0, 0x702);
+        B200FA_WAIT(s_free, 0, 0x703);     // dP^T goes where S^T was once it sits in registers
         tc_fence_after();
-        issue_kmajor(tDP, kV, kDO, 0);
+        issue_kmajor(tWork, kV, kDO, 0);
         umma_commit(dp_full);
         for (int i = 0; i < steps; ++i) {
           const int stage = i % Cfg::kStages;
           const uint32_t stage_lo = stage * kStageLo;
-          // dK += dS^T Q   (A = 16-bit dS^T in the dP^T columns)
+          // dK += dS^T Q   (A = 16-bit dS^T in the work buffer)
+          const uint32_t tDP = tWork + (i & 1) * 128;
           B200FA_WAIT(&q_full[stage], static_cast<uint32_t>((i / Cfg::kStages) & 1), 0x716);
           B200FA_WAIT(ds_full, i & 1, 0x712);
           tc_fence_after();
           TRACE(4, 23);
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
-            const uint32_t a_col = (kk < 4) ? kk * 8 : 64 + (kk - 4) * 8;
+            const uint32_t a_col = (kk >> 1) * 32 + (kk & 1) * 8;
             const uint32_t b_lo = mQ.lo + stage_lo + umma_off(kk * 2048);
             if (kk == 0 && i == 0) umma_ts_fast<false>(tDK, tDP + a_col, b_lo, mQ.hi, idesc_acc);
             else                   umma_ts_fast<true>(tDK, tDP + a_col, b_lo, mQ.hi, idesc_acc);
           }
           umma_commit(&qdo_empty[stage]);   // this lane is done with Q_i (dK) and dO_i (dP^T)
+          umma_commit(&buf_free[i & 1]);
           TRACE(4, 28);
           if (i + 1 < steps) {
-            // dP^T of the next step overwrites dS^T, in issue order behind dK
+            // dP^T of the next step replaces S^T of the next step in the other work buffer
             const int nstage = (i + 1) % Cfg::kStages;
             B200FA_WAIT(&do_full[nstage], static_cast<uint32_t>(((i + 1) / Cfg::kStages) & 1), 0x713);
+            B200FA_WAIT(s_free, (i + 1) & 1, 0x717);
             tc_fence_after();
-            issue_kmajor(tDP, kV, kDO, nstage * kStageLo);
+            issue_kmajor(tWork + ((i + 1) & 1) * 128, kV, kDO, nstage * kStageLo);
             umma_commit(dp_full);
           }
         }
@@ -384,7 +410,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         umma_commit(acc_full);
       }
     }
-  } else if (warp == 11) {
+  } else if (warp == 19) {
     // =========================== TMA producer ===========================
     if (lane == 0) {
       auto load_tile = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int srow, int head) {
@@ -419,7 +445,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
 teardown:
   tc_fence_before();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == 16) {
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
@@ -789,7 +815,7 @@ cudaError_t launch_one(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
   }
   const int tiles = (p.S + kTile - 1) / kTile;
   if (p.parts & 2) {
-    k1<<<dim3(tiles, p.Hkv, p.B), kThreads, Cfg::kSmemBytes, stream>>>(mq, mk, mv, mdo, p);
+    k1<<<dim3(tiles, p.Hkv, p.B), kDkdvThreads, Cfg::kSmemBytes, stream>>>(mq, mk, mv, mdo, p);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }

@@ -362,8 +362,10 @@ int b200fa_bwd_no_alloc(const b200fa_tensor4* q, const b200fa_tensor4* k, const 
   void* scratch = nullptr;
   const int rc = static_scratch_for(device, &scratch);
   if (rc != B200FA_OK) return rc;
+  // parts 7 | 8: the whole backward, every kernel on the caller's stream, so that this entry
+  // point creates no stream or event either
   return bwd_impl(q, k, v, out, dout, lse, dq, dk, dv, scratch, B200FA_NO_ALLOC_SCRATCH_BYTES, dtype, causal, scale,
-                  stream, device, status_word, false);
+                  stream, device, status_word, false, 7 | 8);
 }
 
 }  // extern "C"

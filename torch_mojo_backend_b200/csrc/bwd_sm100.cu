@@ -33,8 +33,20 @@
           (static_cast<unsigned long long>(clock64()) << 8) | (ev);                              \
     }                                                                                            \
   } while (0)
+// per-CTA clock stamps (SM-local clock, plus the SM id) behind the role timelines
+#define CTA_CLOCK(slot)                                                                          \
+  do {                                                                                           \
+    if (p.status != nullptr) {                                                                   \
+      const unsigned long long cta_ =                                                            \
+          blockIdx.x + gridDim.x * (blockIdx.y + static_cast<unsigned long long>(gridDim.y) * blockIdx.z); \
+      unsigned long long* rec_ = reinterpret_cast<unsigned long long*>(p.status + 32848) + cta_ * 8; \
+      rec_[slot] = clock64();                                                                    \
+      if ((slot) == 0) { unsigned sm_; asm volatile("mov.u32 %0, %%smid;" : "=r"(sm_)); rec_[7] = sm_; } \
+    }                                                                                            \
+  } while (0)
 #else
 #define TRACE(role, ev) do {} while (0)
+#define CTA_CLOCK(slot) do {} while (0)
 #endif
 
 namespace b200fa {
@@ -103,7 +115,7 @@ template <int kD, bool kBf16, bool kCausal>
 __global__ void __launch_bounds__(kDkdvThreads, 1)
 bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                 const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
-                const BwdParams p) {
+                const BwdParams p, const int sched_group) {
   using Cfg = BwdCfg<kD>;
   // TMEM: two 128-column work buffers (step i uses buffer i & 1 for S^T, then dP^T, then dS^T),
   // then the dV and dK accumulators.
@@ -135,12 +147,25 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
 #ifdef B200FA_TRACE
   int trace_n = 0;
 #endif
-  const int n_tile = blockIdx.x;
-  const int hk = blockIdx.y;
-  const int b = blockIdx.z;
+  if (threadIdx.x == 0) CTA_CLOCK(0);
+  // Block order: (batch, kv head) pairs are walked `sched_group` at a time, few enough that the
+  // Q / dO rows they stream stay in L2, and inside such a group the K/V tiles with the most
+  // causal work (the earliest) come first, so the last wave of CTAs is made of short ones.
+  const int m_tiles = (p.S + kTile - 1) / kTile;
+  int n_tile, hk, b;
+  {
+    const int pairs = p.B * p.Hkv;
+    const int per_group = sched_group * m_tiles;
+    const int g = static_cast<int>(blockIdx.x) / per_group;
+    const int gsize = min(sched_group, pairs - g * sched_group);
+    const int within = static_cast<int>(blockIdx.x) - g * per_group;
+    n_tile = within / gsize;
+    const int pair = g * sched_group + within % gsize;
+    b = pair / p.Hkv;
+    hk = pair - b * p.Hkv;
+  }
   const int group = p.Hq / p.Hkv;
   const int n0 = n_tile * kTile;
-  const int m_tiles = (p.S + kTile - 1) / kTile;
   const int m_start = kCausal ? n_tile : 0;
   const int per_head = m_tiles - m_start;
   const int steps = group * per_head;
@@ -185,6 +210,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) CTA_CLOCK(1);
 
   if (warp < 16) {
     // =========================== compute warps ===========================
@@ -279,6 +305,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     // ---- epilogue: dV and dK (this warpgroup's quarter of the head dimension)
     B200FA_WAIT(acc_full, 0, 0x520);
     tc_fence_after();
+    if (threadIdx.x == 0) CTA_CLOCK(2);
     {
       const int krow = n0 + j;
       const bool valid = krow < p.S;
@@ -443,12 +470,14 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   }
 
 teardown:
+  if (threadIdx.x == 0) CTA_CLOCK(3);
   tc_fence_before();
   __syncthreads();
   if (warp == 16) {
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
+    if (lane == 0) CTA_CLOCK(4);
   }
 }
 
@@ -491,6 +520,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
 #ifdef B200FA_TRACE
   int trace_n = 0;
 #endif
+  if (threadIdx.x == 0) CTA_CLOCK(0);
   const int m_tiles = (p.S + kTile - 1) / kTile;
   const int m_tile = m_tiles - 1 - static_cast<int>(blockIdx.x);  // heaviest (latest) causal tiles first
   const int h = blockIdx.y;
@@ -536,6 +566,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) CTA_CLOCK(1);
 
   if (warp < 8) {
     // =========================== compute warps ===========================
@@ -596,6 +627,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
     // ---- epilogue: dQ (this warpgroup's half of the head dimension)
     B200FA_WAIT(acc_full, 0, 0x920);
     tc_fence_after();
+    if (threadIdx.x == 0) CTA_CLOCK(2);
     {
       const int qrow = m0 + r;
       const bool valid = qrow < p.S;
@@ -721,12 +753,14 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
   }
 
 teardown:
+  if (threadIdx.x == 0) CTA_CLOCK(3);
   tc_fence_before();
   __syncthreads();
   if (warp == 8) {
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
+    if (lane == 0) CTA_CLOCK(4);
   }
 }
 #undef B200FA_WAIT
@@ -788,6 +822,32 @@ __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const BwdParams p) 
   }
 }
 
+// The dK/dV kernel and the dQ kernel only depend on the preprocess kernel, not on each other.
+// Run back to back on one stream, the second cannot start until the last, partly idle wave of
+// the first has drained; forked onto a side stream its CTAs fill those SMs as they free up.
+// One side stream and one fork/join event pair per host thread and device, created on first
+// use and kept for the life of the thread.
+struct SideStream {
+  cudaStream_t stream = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+  bool tried = false;
+};
+SideStream* side_stream_for(int dev) {
+  thread_local SideStream side[16];
+  if (dev < 0 || dev >= 16) return nullptr;
+  SideStream& s = side[dev];
+  if (!s.tried) {
+    s.tried = true;
+    if (cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) != cudaSuccess) {
+      cudaGetLastError();
+      s.stream = nullptr;
+    }
+  }
+  return s.stream ? &s : nullptr;
+}
+
 template <int kD, bool kBf16, bool kCausal>
 cudaError_t launch_one(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mdo,
                        const BwdParams& p, cudaStream_t stream) {
@@ -814,14 +874,37 @@ cudaError_t launch_one(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
     attr_set[dev] = true;
   }
   const int tiles = (p.S + kTile - 1) / kTile;
+  // fork: the dQ kernel goes to the side stream, behind everything enqueued so far.  Only
+  // causal problems: their CTAs differ in length, which is what leaves a long partly idle tail;
+  // with equal CTAs the tail is short and interleaving the two kernels only costs L2 hits.
+  SideStream* side = (kCausal && (p.parts & 6) == 6 && !(p.parts & 8)) ? side_stream_for(dev) : nullptr;
+  if (side) {
+    e = cudaEventRecord(side->fork, stream);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(side->stream, side->fork, 0);
+    if (e != cudaSuccess) return e;
+  }
   if (p.parts & 2) {
-    k1<<<dim3(tiles, p.Hkv, p.B), kDkdvThreads, Cfg::kSmemBytes, stream>>>(mq, mk, mv, mdo, p);
+    // (batch, kv head) pairs whose streamed Q / dO rows (both, all query heads of the pair)
+    // add up to about 48 MiB share a scheduling group
+    const int64_t pair_bytes = static_cast<int64_t>(p.Hq / p.Hkv) * p.S * p.D * 2 * 2;
+    int64_t sched_group = (48ll << 20) / (pair_bytes > 0 ? pair_bytes : 1);
+    const int64_t pairs = static_cast<int64_t>(p.B) * p.Hkv;
+    if (sched_group < 1) sched_group = 1;
+    if (sched_group > pairs) sched_group = pairs;
+    k1<<<static_cast<unsigned>(tiles * pairs), kDkdvThreads, Cfg::kSmemBytes, stream>>>(
+        mq, mk, mv, mdo, p, static_cast<int>(sched_group));
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }
   if (p.parts & 4) {
-    k2<<<dim3(tiles, p.Hq, p.B), kThreads, Cfg::kSmemBytes, stream>>>(mq, mk, mv, mdo, p);
+    k2<<<dim3(tiles, p.Hq, p.B), kThreads, Cfg::kSmemBytes, side ? side->stream : stream>>>(mq, mk, mv, mdo, p);
     e = cudaGetLastError();
+  }
+  if (side) {
+    // join: the caller's stream continues only after both kernels
+    cudaError_t e2 = cudaEventRecord(side->join, side->stream);
+    if (e2 == cudaSuccess) e2 = cudaStreamWaitEvent(stream, side->join, 0);
+    if (e == cudaSuccess) e = e2;
   }
   return e;
 }

@@ -34,7 +34,8 @@ struct BwdParams {
   float scale;
   float scale_log2;
   uint32_t* status;
-  int parts;  // bit 0 preprocess, bit 1 dK/dV kernel, bit 2 dQ kernel (7 = the whole backward)
+  int parts;  // bit 0 preprocess, bit 1 dK/dV kernel, bit 2 dQ kernel (7 = the whole backward);
+              // bit 3: keep every kernel on the caller's stream (no side stream, nothing created)
 };
 
 // dtype tags shared with the C header

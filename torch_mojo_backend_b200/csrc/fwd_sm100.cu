@@ -33,8 +33,19 @@
           (static_cast<unsigned long long>(clock64()) << 8) | (ev);                              \
     }                                                                                            \
   } while (0)
+// per-CTA clock stamps (SM-local clock, plus the SM id) behind the role timelines
+#define CTA_CLOCK(slot)                                                                          \
+  do {                                                                                           \
+    if (p.status != nullptr) {                                                                   \
+      unsigned long long* rec_ = reinterpret_cast<unsigned long long*>(p.status + 32848) +      \
+                                 static_cast<unsigned long long>(blockIdx.x) * 8;                \
+      rec_[slot] = clock64();                                                                    \
+      if ((slot) == 0) { unsigned sm_; asm volatile("mov.u32 %0, %%smid;" : "=r"(sm_)); rec_[7] = sm_; } \
+    }                                                                                            \
+  } while (0)
 #else
 #define TRACE(role, ev) do {} while (0)
+#define CTA_CLOCK(slot) do {} while (0)
 #endif
 
 namespace b200fa {
@@ -123,6 +134,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
   int trace_n = 0;
 #endif
 
+  if (threadIdx.x == 0) CTA_CLOCK(0);
   // ---- which (pair, head, batch) this CTA owns: head groups keep K/V in L2, and inside a
   // group the heaviest (latest) causal pairs are scheduled first.
   const int total_bh = p.B * p.Hq;
@@ -155,7 +167,31 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
   }
   const int n_max = max(n_t[0], n_t[1]);
 
-  if (threadIdx.x == 0) {
+  // Lane 0 of the producer warp sets up the barriers and at once issues the loads that need
+  // no free slot (Q, and K/V up to the depth of the ring), so that their latency overlaps the
+  // TMEM allocation and the block-wide synchronisation below.
+  auto load_tile = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int srow, int head) {
+    mbar_arrive_expect_tx(bar, Cfg::kTileBytes);
+#pragma unroll
+    for (int cs = 0; cs < Cfg::kSub; ++cs) {
+      tma_load_4d(dst + cs * kSubTileBytes, map, bar, cs * 64, srow, head, b);
+    }
+  };
+  // K/V ring entry `seq`: K_j for even seq, V_j for odd, j = seq / 2; Q rides along with K_0
+  auto produce = [&](int seq) {
+    const int slot = seq % Cfg::kStages;
+    const int j = seq >> 1;
+    if (seq == 0) {
+      // Q tile 0 rides ahead of K_0, Q tile 1 right behind it
+      if (n_t[0] > 0) load_tile(&mapQ, sQ, &q_full[0], row0, h);
+      load_tile(&mapK, sKV + slot * Cfg::kTileBytes, &kv_full[slot], 0, hk);
+      if (n_t[1] > 0) load_tile(&mapQ, sQ + Cfg::kTileBytes, &q_full[1], row0 + kBM, h);
+    } else {
+      load_tile((seq & 1) ? &mapV : &mapK, sKV + slot * Cfg::kTileBytes, &kv_full[slot], j * kBN, hk);
+    }
+  };
+  const int n_loads = 2 * n_max;
+  if (warp == 14 && lane == 0) {
     mbar_init(&q_full[0], 1);
     mbar_init(&q_full[1], 1);
     for (int i = 0; i < Cfg::kStages; ++i) {
@@ -176,20 +212,17 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
     *abort_flag = 0;
     fence_mbar_init();
     fence_proxy_async_smem();
+    for (int seq = 0; seq < min(n_loads, Cfg::kStages); ++seq) produce(seq);
   }
   if (warp == 12) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
-  if (warp == 14 && lane == 0) {
-    tma_prefetch_desc(&mapQ);
-    tma_prefetch_desc(&mapK);
-    tma_prefetch_desc(&mapV);
-  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) CTA_CLOCK(1);
 
 #define B200FA_WAIT(bar, parity, site) \
   if (!mbar_wait((bar), (parity), abort_flag, p.status, (site))) goto teardown
@@ -508,31 +541,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
       }
     } else if (warp == 14) {
       // =========================== TMA producer ===========================
-      if (lane == 0 && n_max > 0) {
-        int seq = 0;
-        auto load_tile = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int srow, int head) {
-          mbar_arrive_expect_tx(bar, Cfg::kTileBytes);
-#pragma unroll
-          for (int cs = 0; cs < Cfg::kSub; ++cs) {
-            tma_load_4d(dst + cs * kSubTileBytes, map, bar, cs * 64, srow, head, b);
-          }
-        };
-        for (int j = 0; j < n_max; ++j) {
-          for (int which = 0; which < 2; ++which) {  // 0 = K_j, 1 = V_j
-            const int slot = seq % Cfg::kStages;
-            if (seq >= Cfg::kStages) {
-              B200FA_WAIT(&kv_empty[slot], ((seq / Cfg::kStages) - 1) & 1, 0x400);
-            }
-            if (j == 0 && which == 0) {
-              // Q tile 0 rides ahead of K_0, Q tile 1 right behind it
-              if (n_t[0] > 0) load_tile(&mapQ, sQ, &q_full[0], row0, h);
-              load_tile(&mapK, sKV + slot * Cfg::kTileBytes, &kv_full[slot], j * kBN, hk);
-              if (n_t[1] > 0) load_tile(&mapQ, sQ + Cfg::kTileBytes, &q_full[1], row0 + kBM, h);
-            } else {
-              load_tile(which == 0 ? &mapK : &mapV, sKV + slot * Cfg::kTileBytes, &kv_full[slot], j * kBN, hk);
-            }
-            ++seq;
-          }
+      if (lane == 0) {
+        // the first kStages entries went out before the block-wide synchronisation
+        for (int seq = Cfg::kStages; seq < n_loads; ++seq) {
+          B200FA_WAIT(&kv_empty[seq % Cfg::kStages], ((seq / Cfg::kStages) - 1) & 1, 0x400);
+          produce(seq);
         }
       }
     }
@@ -540,12 +553,15 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
 
 teardown:
 #undef B200FA_WAIT
+  if (threadIdx.x == 0) CTA_CLOCK(2);    // softmax of tile 0 finished
+  if (threadIdx.x == 256) CTA_CLOCK(3);  // correction warps finished the last epilogue
   tc_fence_before();
   __syncthreads();
   if (warp == 12) {
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
+    if (lane == 0) CTA_CLOCK(4);
   }
 }
 

@@ -212,6 +212,52 @@ def test_unsynchronised_bursts_are_deterministic():
         assert torch.equal(out, outs[0][0]) and torch.equal(lse, outs[0][1])
 
 
+def test_backward_bursts_on_a_side_torch_stream_are_deterministic():
+    """The causal backward forks one kernel onto a library-owned stream and joins it back:
+    un-synchronised bursts on a non-default caller stream must still see their inputs and
+    give bitwise identical gradients."""
+    q, k, v, do = rand_case(torch.bfloat16, 2, 8, 2, 1024, 128, seed=11)
+    qc, kc, vc, doc = q.cuda(), k.cuda(), v.cuda(), do.cuda()
+    ref_out, ref_lse = raw.flash_fwd(qc, kc, vc, causal=True)
+    ref = raw.flash_bwd(doc, qc, kc, vc, ref_out, ref_lse, causal=True)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    grads = []
+    with torch.cuda.stream(side):
+        for _ in range(6):
+            out, lse = raw.flash_fwd(qc, kc, vc, causal=True)
+            grads.append(raw.flash_bwd(doc, qc, kc, vc, out, lse, causal=True))
+    side.synchronize()
+    for dq, dk, dv in grads:
+        assert torch.equal(dq, ref[0]) and torch.equal(dk, ref[1]) and torch.equal(dv, ref[2])
+
+
+def test_forward_and_backward_replay_from_a_cuda_graph():
+    """Both directions are plain stream work (the backward's fork and join are events), so a
+    step captured into a CUDA graph replays to the same bits as the eager calls."""
+    q, k, v, do = rand_case(torch.bfloat16, 1, 8, 4, 512, 128, seed=12)
+    qc, kc, vc, doc = q.cuda(), k.cuda(), v.cuda(), do.cuda()
+    out, lse = raw.flash_fwd(qc, kc, vc, causal=True)
+    eager = raw.flash_bwd(doc, qc, kc, vc, out, lse, causal=True)   # also creates the side stream outside capture
+    torch.cuda.synchronize()
+    g_out, g_lse = torch.empty_like(out), torch.empty_like(lse)
+    g_dq, g_dk, g_dv = (torch.empty_like(t) for t in eager)
+    need = _lib.bwd_workspace_bytes(1, 8, 4, 512, 128, raw.dtype_code(torch.bfloat16))
+    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        raw.flash_fwd(qc, kc, vc, causal=True, out=g_out, lse=g_lse)
+        raw.flash_bwd(doc, qc, kc, vc, g_out, g_lse, causal=True, dq=g_dq, dk=g_dk, dv=g_dv, workspace=ws)
+    for _ in range(2):
+        for t in (g_out, g_lse, g_dq, g_dk, g_dv):
+            t.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(g_out, out) and torch.equal(g_lse, lse)
+        assert torch.equal(g_dq, eager[0]) and torch.equal(g_dk, eager[1]) and torch.equal(g_dv, eager[2])
+
+
 def test_rejected_calls_launch_nothing():
     q = torch.zeros(1, 2, 128, 96, dtype=torch.bfloat16, device="cuda")
     before = _lib.launch_count()

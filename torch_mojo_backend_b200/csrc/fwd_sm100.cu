@@ -10,7 +10,8 @@
 //
 //   warps 0-3   softmax of query tile 0   (thread i <-> TMEM lane i <-> query row i)
 //   warps 4-7   softmax of query tile 1
-//   warps 8-11  correction: rescale O in TMEM when a row max moved, final O/l + LSE epilogue
+//   warps 8-11  correction: rescale O in TMEM when a row max moved; epilogue: O / l staged in
+//               shared memory and written with TMA stores, LSE
 //   warps 12-13 MMA issuers, one per query tile (one elected lane each issues tcgen05.mma / commit)
 //   warp  14    TMA producer (Q once, then a ring of K/V tiles)
 //   warp  15    idle (it only donates registers)
@@ -106,7 +107,8 @@ struct FwdSched {
 template <int kD, bool kBf16, bool kCausal>
 __global__ void __launch_bounds__(kThreads, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
-           const __grid_constant__ CUtensorMap mapV, const FwdParams p, const FwdSched sched) {
+           const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapO, const FwdParams p,
+           const FwdSched sched) {
   using Cfg = FwdCfg<kD>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -204,7 +206,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
       mbar_init(&p_full[t * 2], 8);      // 4 softmax warps (P half 0) + 4 correction warps (O ready)
       mbar_init(&p_full[t * 2 + 1], 4);
       mbar_init(&o_full[t], 1);
-      mbar_init(&o_ready[t], 4);         // unused: "O ready" is folded into p_full[t][0]
+      mbar_init(&o_ready[t], 4);         // the four correction warps have staged the output tile
       mbar_init(&sc_full[t], 4);
       mbar_init(&sc_empty[t], 4);
       mbar_init(&turn[t], 1);
@@ -346,30 +348,41 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
       const float inv_l = 1.f / l;
       const int q_row = row0 + t * kBM + row;
       const uint32_t tO = tmem_base + lane_off + (t == 0 ? Cfg::kTmemO0 : Cfg::kTmemO1);
-      const bool valid = q_row < p.Sq;
-      uint16_t* orow = reinterpret_cast<uint16_t*>(p.out.ptr) +
-                       (static_cast<int64_t>(b) * p.out.sb + static_cast<int64_t>(h) * p.out.sh +
-                        static_cast<int64_t>(q_row) * p.out.ss);
+      // The 16-bit output tile is staged in this query tile's own Q buffer (every MMA that
+      // read it has completed), in the swizzled box layout, and leaves through TMA stores:
+      // whole 128-byte lines, nothing for the CTA to wait on but the read of shared memory,
+      // and rows past the end of the sequence are clipped by the tensor map.
+      uint8_t* stage = sQ + t * Cfg::kTileBytes;
 #pragma unroll
       for (int cidx = 0; cidx < kD / 32; ++cidx) {
         uint32_t o[32];
         tmem_ld32(tO + cidx * 32, o);
         tmem_wait_ld();
-        if (valid) {
-          const float* of = reinterpret_cast<const float*>(o);
+        const float* of = reinterpret_cast<const float*>(o);
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint4 w;
-            w.x = pack2<kBf16>(of[v * 8 + 0] * inv_l, of[v * 8 + 1] * inv_l);
-            w.y = pack2<kBf16>(of[v * 8 + 2] * inv_l, of[v * 8 + 3] * inv_l);
-            w.z = pack2<kBf16>(of[v * 8 + 4] * inv_l, of[v * 8 + 5] * inv_l);
-            w.w = pack2<kBf16>(of[v * 8 + 6] * inv_l, of[v * 8 + 7] * inv_l);
-            *reinterpret_cast<uint4*>(orow + cidx * 32 + v * 8) = w;
-          }
+        for (int v = 0; v < 4; ++v) {
+          uint4 w;
+          w.x = pack2<kBf16>(of[v * 8 + 0] * inv_l, of[v * 8 + 1] * inv_l);
+          w.y = pack2<kBf16>(of[v * 8 + 2] * inv_l, of[v * 8 + 3] * inv_l);
+          w.z = pack2<kBf16>(of[v * 8 + 4] * inv_l, of[v * 8 + 5] * inv_l);
+          w.w = pack2<kBf16>(of[v * 8 + 6] * inv_l, of[v * 8 + 7] * inv_l);
+          const int chunk = cidx * 4 + v;   // 16-byte chunk of the row
+          *reinterpret_cast<uint4*>(stage + (chunk >> 3) * kSubTileBytes + row * 128 +
+                                    (((chunk & 7) ^ (row & 7)) << 4)) = w;
         }
       }
-      if (valid) {
+      fence_proxy_async_smem();
+      mbar_arrive_warp(&o_ready[t]);
+      if (q_row < p.Sq) {
         p.lse[(static_cast<int64_t>(b) * p.Hq + h) * p.Sq + q_row] = m * p.scale + logf(l);
+      }
+      if (warp == 8 && lane == 0) {
+        if (!mbar_wait(&o_ready[t], 0, abort_flag, p.status, 0x218 + t)) return false;
+#pragma unroll
+        for (int cs = 0; cs < Cfg::kSub; ++cs) {
+          tma_store_4d(&mapO, stage + cs * kSubTileBytes, cs * 64, row0 + t * kBM, h, b);
+        }
+        tma_store_commit();
       }
       return true;
     };
@@ -553,6 +566,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
 
 teardown:
 #undef B200FA_WAIT
+  // the staged output tiles must have been read before shared memory is given back
+  if (warp == 8 && lane == 0) tma_store_wait_read();
   if (threadIdx.x == 0) CTA_CLOCK(2);    // softmax of tile 0 finished
   if (threadIdx.x == 256) CTA_CLOCK(3);  // correction warps finished the last epilogue
   tc_fence_before();
@@ -566,8 +581,8 @@ teardown:
 }
 
 template <int kD, bool kBf16, bool kCausal>
-cudaError_t launch_one(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FwdParams& p,
-                       const FwdSched& sched, cudaStream_t stream) {
+cudaError_t launch_one(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
+                       const FwdParams& p, const FwdSched& sched, cudaStream_t stream) {
   using Cfg = FwdCfg<kD>;
   auto kern = fwd_kernel<kD, kBf16, kCausal>;
   static bool attr_set[16] = {};  // per device
@@ -579,7 +594,7 @@ cudaError_t launch_one(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
     attr_set[dev] = true;
   }
   const int grid = sched.npairs * p.B * p.Hq;
-  kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(mq, mk, mv, p, sched);
+  kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(mq, mk, mv, mo, p, sched);
   return cudaGetLastError();
 }
 
@@ -587,10 +602,11 @@ cudaError_t launch_one(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
 
 cudaError_t launch_fwd_sm100(const FwdParams& p, int dtype, cudaStream_t stream, int* launches) {
   const bool bf16 = (dtype == kBF16);
-  CUtensorMap mq, mk, mv;
+  CUtensorMap mq, mk, mv, mo;
   if (!encode_map_16bit(&mq, p.q, p.B, p.Hq, p.Sq, p.D, kBM, bf16)) return cudaErrorInvalidValue;
   if (!encode_map_16bit(&mk, p.k, p.B, p.Hkv, p.Sk, p.D, kBN, bf16)) return cudaErrorInvalidValue;
   if (!encode_map_16bit(&mv, p.v, p.B, p.Hkv, p.Sk, p.D, kBN, bf16)) return cudaErrorInvalidValue;
+  if (!encode_map_16bit(&mo, p.out, p.B, p.Hq, p.Sq, p.D, kBM, bf16)) return cudaErrorInvalidValue;
   FwdSched sched;
   sched.npairs = (p.Sq + 2 * kBM - 1) / (2 * kBM);
   sched.nkv_total = (p.Sk + kBN - 1) / kBN;
@@ -602,7 +618,7 @@ cudaError_t launch_fwd_sm100(const FwdParams& p, int dtype, cudaStream_t stream,
   if (group > total_bh) group = total_bh;
   sched.group = static_cast<int>(group);
   cudaError_t e;
-#define B200FA_DISPATCH(D_, BF_, C_) e = launch_one<D_, BF_, C_>(mq, mk, mv, p, sched, stream)
+#define B200FA_DISPATCH(D_, BF_, C_) e = launch_one<D_, BF_, C_>(mq, mk, mv, mo, p, sched, stream)
   if (p.D == 128) {
     if (bf16) { if (p.causal) B200FA_DISPATCH(128, true, true); else B200FA_DISPATCH(128, true, false); }
     else      { if (p.causal) B200FA_DISPATCH(128, false, true); else B200FA_DISPATCH(128, false, false); }

@@ -64,3 +64,35 @@ def test_world_size_two_gather_matches_unsharded(tmp_path):
     mp.spawn(_worker, args=(2, _free_port(), path), nprocs=2, join=True)
     res = torch.load(path)
     assert res["err"] < 1e-6 and res["max"] == 2.0
+
+
+def _leaver_worker(rank, world, port, result_path):
+    """Rank 1 leaves between steps (after a completed gather, before the next one); rank 0 must
+    learn of it from a bounded collective, on the host, and report instead of waiting forever."""
+    import datetime
+
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    t = torch.tensor([float(rank)])
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)   # step 0 completes on every rank
+    if rank == 1:
+        os._exit(0)                             # gone before step 1, nothing of its own in flight
+    detected = ""
+    try:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    except Exception as exc:  # gloo reports a closed connection or its timeout
+        detected = type(exc).__name__
+    torch.save({"first": t.item(), "detected": detected}, result_path)
+    os._exit(0)                                 # the group is broken; skip its teardown
+
+
+def test_rank_that_leaves_before_the_gather_is_detected_on_the_host(tmp_path):
+    path = str(tmp_path / "leaver.pt")
+    ctx = mp.spawn(_leaver_worker, args=(2, _free_port(), path), nprocs=2, join=False)
+    for p in ctx.processes:
+        p.join(60)
+        assert not p.is_alive(), "a rank is still waiting on a peer that left"
+    res = torch.load(path)
+    assert res["first"] == 1.0
+    assert res["detected"], "the surviving rank did not notice the missing peer"

@@ -21,10 +21,6 @@
 #include "common.cuh"
 #include "ptx.cuh"
 
-#ifndef B200FA_ABL
-#define B200FA_ABL 0
-#endif
-
 #ifdef B200FA_TRACE
 // debug timeline: role r appends (event, clock) records for CTA 0 into the buffer behind the status word
 #define TRACE(role, ev)                                                                          \
@@ -248,16 +244,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
       tc_fence_after();
       if ((warp & 3) == 0) TRACE(t, 1);
       uint32_t s[128];
-      if (B200FA_ABL & 16) {
-#pragma unroll
-        for (int i = 0; i < 128; ++i) s[i] = __float_as_uint(0.001f * (i + row));
-      } else {
-        tmem_ld32(tS + 0, s + 0);
-        tmem_ld32(tS + 32, s + 32);
-        tmem_ld32(tS + 64, s + 64);
-        tmem_ld32(tS + 96, s + 96);
-        tmem_wait_ld();
-      }
+      tmem_ld32(tS + 0, s + 0);
+      tmem_ld32(tS + 32, s + 32);
+      tmem_ld32(tS + 64, s + 64);
+      tmem_ld32(tS + 96, s + 96);
+      tmem_wait_ld();
       float* sf = reinterpret_cast<float*>(s);
       if ((warp & 3) == 0) TRACE(t, 2);
       const int col0 = j * kBN;
@@ -273,7 +264,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
       // row max, four independent chains
       float mx0 = sf[0], mx1 = sf[1], mx2 = sf[2], mx3 = sf[3];
 #pragma unroll
-      for (int i = 4; i < ((B200FA_ABL & 2) ? 8 : 128); i += 4) {
+      for (int i = 4; i < 128; i += 4) {
         mx0 = fmaxf(mx0, sf[i]);
         mx1 = fmaxf(mx1, sf[i + 1]);
         mx2 = fmaxf(mx2, sf[i + 2]);
@@ -304,9 +295,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
         for (int i = half * 32; i < half * 32 + 32; ++i) {
           const float2 x = __ffma2_rn(make_float2(sf[2 * i], sf[2 * i + 1]), c2, nmc2);
           float2 pv;
-          if (B200FA_ABL & 1) {
-            pv = x;
-          } else if ((i & 7) < kEmuOf8) {
+          if ((i & 7) < kEmuOf8) {
             pv = exp2_emulated2(x);
           } else {
             pv = make_float2(ex2_approx(x.x), ex2_approx(x.y));
@@ -314,10 +303,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
           if (i & 1) rsb = __fadd2_rn(rsb, pv); else rsa = __fadd2_rn(rsa, pv);
           pk[i] = pack2<kBf16>(pv.x, pv.y);
         }
-        if (!(B200FA_ABL & 8)) {
-          tmem_st32(tS + half * 32, pk + half * 32);
-          tmem_wait_st();
-        }
+        tmem_st32(tS + half * 32, pk + half * 32);
+        tmem_wait_st();
         tc_fence_before();
         mbar_arrive_warp(&p_full[t * 2 + half]);
         if ((warp & 3) == 0) TRACE(t, 4 + half);

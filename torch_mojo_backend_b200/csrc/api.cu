@@ -250,7 +250,6 @@ static int bwd_impl(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   p.dpsum = reinterpret_cast<float*>(ws);
   p.lse_log2 = reinterpret_cast<float*>(ws + align256(rows * 4));
-  p.dq_accum = nullptr;  // no global dQ accumulation: the dQ kernel keeps its accumulator in TMEM
   p.lse = lse;
   p.B = static_cast<int>(B); p.Hq = static_cast<int>(Hq); p.Hkv = static_cast<int>(Hkv);
   p.S = static_cast<int>(S); p.Spad = static_cast<int>(spad); p.D = static_cast<int>(D);

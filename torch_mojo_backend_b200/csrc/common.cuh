@@ -28,7 +28,6 @@ struct BwdParams {
   const float* lse;  // (B, Hq, S) fp32 contiguous (natural log)
   float* dpsum;      // workspace: (B, Hq, Spad) rowsum(dO * O)
   float* lse_log2;   // workspace: (B, Hq, Spad) lse * log2(e)
-  float* dq_accum;   // unused (kept for layout stability): dQ accumulates in tensor memory
   int B, Hq, Hkv, S, Spad, D;
   int causal;
   float scale;

@@ -166,8 +166,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
   const int n_max = max(n_t[0], n_t[1]);
 
   // Lane 0 of the producer warp sets up the barriers and at once issues the loads that need
-  // no free slot (Q, and K/V up to the depth of the ring), so that their latency overlaps the
-  // TMEM allocation and the block-wide synchronisation below.
+  // no free slot and are needed first (Q, K_0, V_0), so that their latency overlaps the TMEM
+  // allocation and the block-wide synchronisation below.
   auto load_tile = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int srow, int head) {
     mbar_arrive_expect_tx(bar, Cfg::kTileBytes);
 #pragma unroll
@@ -189,6 +189,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
     }
   };
   const int n_loads = 2 * n_max;
+  constexpr int kEarlyLoads = 2;   // Q, K_0 and V_0: what the first MMAs wait for; more would only delay the sync
   if (warp == 14 && lane == 0) {
     mbar_init(&q_full[0], 1);
     mbar_init(&q_full[1], 1);
@@ -210,7 +211,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
     *abort_flag = 0;
     fence_mbar_init();
     fence_proxy_async_smem();
-    for (int seq = 0; seq < min(n_loads, Cfg::kStages); ++seq) produce(seq);
+    for (int seq = 0; seq < min(n_loads, kEarlyLoads); ++seq) produce(seq);
   }
   if (warp == 12) {
     tmem_alloc(tmem_slot, 512);
@@ -542,9 +543,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
     } else if (warp == 14) {
       // =========================== TMA producer ===========================
       if (lane == 0) {
-        // the first kStages entries went out before the block-wide synchronisation
-        for (int seq = Cfg::kStages; seq < n_loads; ++seq) {
-          B200FA_WAIT(&kv_empty[seq % Cfg::kStages], ((seq / Cfg::kStages) - 1) & 1, 0x400);
+        // the first kEarlyLoads entries went out before the block-wide synchronisation
+        for (int seq = kEarlyLoads; seq < n_loads; ++seq) {
+          if (seq >= Cfg::kStages) {
+            B200FA_WAIT(&kv_empty[seq % Cfg::kStages], ((seq / Cfg::kStages) - 1) & 1, 0x400);
+          }
           produce(seq);
         }
       }

@@ -64,7 +64,9 @@ typedef struct b200fa_tensor4 {
  * Forward: out = softmax(scale * q k^T [+ causal mask]) v,  lse = logsumexp of the scaled,
  * masked scores (natural log), fp32, contiguous (B, Hq, Sq).
  *   q, out : (B, Hq, Sq, D);  k, v : (B, Hkv, Sk, D) with Hq % Hkv == 0 (query head h reads
- *   key/value head h / (Hq / Hkv));  Sq == Sk;  D in {64, 128}.
+ *   key/value head h / (Hq / Hkv));  D in {64, 128};  Sq == Sk when causal (a causal mask over
+ *   Sq != Sk has a top-left and a bottom-right convention, neither is offered), any Sq, Sk
+ *   otherwise, which the reference's gate does not serve (aten_fast.py:7029-7030).
  *   dtype  : B200FA_BF16 / B200FA_F16 run the tcgen05 tensor-core kernel,
  *            B200FA_F32 runs an exact-fp32 SIMT kernel.
  * Replaces flash_attention_fwd_<dtype>_d<D>_causal{,_strided_qkv,_bhsd}

@@ -67,7 +67,7 @@ FAKE = 0x7F0000000000  # never dereferenced: validation rejects the call first
         (dict(dtype=7), _lib.ERR_BAD_DTYPE),
         (dict(q_shape=(1, 2, 128, 96)), _lib.ERR_UNSUPPORTED),  # head_dim not 64/128
         (dict(k_shape=(1, 3, 128, 64), q_shape=(1, 4, 128, 64)), _lib.ERR_BAD_SHAPE),  # Hq % Hkv
-        (dict(k_shape=(1, 2, 256, 64)), _lib.ERR_UNSUPPORTED),  # Sq != Sk
+        (dict(k_shape=(1, 2, 256, 64)), _lib.ERR_UNSUPPORTED),  # Sq != Sk under a causal mask
         (dict(scale=0.0), _lib.ERR_UNSUPPORTED),
         (dict(scale=float("nan")), _lib.ERR_UNSUPPORTED),
         (dict(q_stride=(16384, 8192, 64, 2)), _lib.ERR_BAD_STRIDE),  # head_dim stride must be 1

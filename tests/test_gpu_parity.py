@@ -83,6 +83,54 @@ def test_forward_backward_match_oracle(dtype, B, Hq, Hkv, S, D, causal):
     assert dk.shape == (B, Hkv, S, D)
 
 
+CROSS = [
+    # dtype, B, Hq, Hkv, Sq, Sk, D: unmasked attention over a key sequence of another length
+    # (decode-like single query row, short query over a long context, long query over few keys)
+    (torch.bfloat16, 2, 4, 4, 1, 1000, 128),
+    (torch.bfloat16, 1, 8, 2, 384, 1024, 128),
+    (torch.float16, 2, 4, 2, 1000, 200, 64),
+    (torch.bfloat16, 1, 2, 2, 130, 65, 64),
+    (torch.float32, 1, 4, 2, 96, 320, 64),
+]
+
+
+@pytest.mark.parametrize("dtype,B,Hq,Hkv,Sq,Sk,D", CROSS)
+def test_unmasked_attention_over_another_key_length(dtype, B, Hq, Hkv, Sq, Sk, D):
+    """Beyond the reference's gate (it needs Sq == Sk): without a mask there is no alignment
+    question, so any pair of lengths is served, forward and backward."""
+    g = torch.Generator().manual_seed(20260901 + Sq + Sk)
+    q = (torch.randn(B, Hq, Sq, D, generator=g) * 0.5).to(dtype)
+    k = (torch.randn(B, Hkv, Sk, D, generator=g) * 0.5).to(dtype)
+    v = (torch.randn(B, Hkv, Sk, D, generator=g) * 0.5).to(dtype)
+    dout = torch.randn(B, Hq, Sq, D, generator=g).to(dtype)
+    scale = D ** -0.5
+    ref_out, ref_lse = O.sdpa_forward(q, k, v, False, scale)
+    _, rdq, rdk, rdv = O.sdpa_backward(q, k, v, dout, False, scale)
+    out, lse, dq, dk, dv = run_gpu(q, k, v, dout, False, scale)
+    tol = tol_for(dtype)
+    assert_within("out", out, ref_out, tol, dtype)
+    assert_within("lse", lse, ref_lse, TOL_LSE)
+    assert_within("dq", dq, rdq, tol, dtype)
+    assert_within("dk", dk, rdk, tol, dtype)
+    assert_within("dv", dv, rdv, tol, dtype)
+    assert dq.shape == (B, Hq, Sq, D) and dk.shape == (B, Hkv, Sk, D) and dv.shape == (B, Hkv, Sk, D)
+    if dtype != torch.float32:
+        # the exact-fp32 SIMT kernels on the same 16-bit inputs agree too
+        s_out, s_lse, s_dq, s_dk, s_dv = run_gpu(q, k, v, dout, False, scale, simt=True)
+        assert_within("simt out", s_out, ref_out, tol, dtype)
+        assert_within("simt dk", s_dk, rdk, tol, dtype)
+        assert_within("simt dq", s_dq, rdq, tol, dtype)
+
+
+def test_causal_mask_over_unequal_lengths_is_refused():
+    q = torch.zeros(1, 2, 128, 64, dtype=torch.bfloat16, device="cuda")
+    k = torch.zeros(1, 2, 256, 64, dtype=torch.bfloat16, device="cuda")
+    before = _lib.launch_count()
+    with pytest.raises(_lib.B200FAError):
+        raw.flash_fwd(q, k, k, causal=True)
+    assert _lib.launch_count() == before
+
+
 @pytest.mark.parametrize("name", golden_names())
 def test_golden_fixtures(name):
     meta, q, k, v, dout, exp = load_golden(name)

@@ -46,8 +46,9 @@ def test_ineligible_regimes_never_reach_the_bridge(host_backed_mojo):
     with pytest.raises(NotImplementedError):  # head_dim 96
         x = mojo((1, 2, 128, 96))
         torch.nn.functional.scaled_dot_product_attention(x, x, x, is_causal=True)
-    with pytest.raises(NotImplementedError):  # Sq != Sk
-        torch.nn.functional.scaled_dot_product_attention(q, mojo((1, 2, 64, 64)), mojo((1, 2, 64, 64)))
+    with pytest.raises(NotImplementedError):  # Sq != Sk under a causal mask: two conventions, none served
+        torch.nn.functional.scaled_dot_product_attention(q, mojo((1, 2, 64, 64)), mojo((1, 2, 64, 64)),
+                                                         is_causal=True)
     with pytest.raises(NotImplementedError):  # GQA shapes without enable_gqa
         torch.nn.functional.scaled_dot_product_attention(mojo((1, 4, 128, 64)), q, q, is_causal=True)
     with pytest.raises(NotImplementedError):  # mixed dtypes
@@ -65,6 +66,22 @@ def test_gate_is_metadata_only_and_accepts_all_dtypes(host_backed_mojo):
         got = flash_ops.flash_inputs(q, k, k, None, 0.0, False, None, enable_gqa=True)
         assert got is not None and got[0] is q
     assert host_backed_mojo.calls == []
+
+
+def test_cross_attention_lengths_reach_the_bridge_when_unmasked(host_backed_mojo):
+    spy = host_backed_mojo
+    q, k, v = mojo((1, 4, 96, 64)), mojo((1, 2, 320, 64)), mojo((1, 2, 320, 64))
+    res = torch.ops.aten._scaled_dot_product_flash_attention.default(q, k, v, 0.0, False, False)
+    (kind, a), = spy.calls
+    assert kind == "fwd" and a["causal"] is False
+    assert tuple(a["q"].shape) == (1, 4, 96, 64) and tuple(a["k"].shape) == (1, 2, 320, 64)
+    assert tuple(res[0].shape) == (1, 4, 96, 64) and tuple(res[1].shape) == (1, 4, 96)
+    assert (res[4], res[5]) == (96, 320)
+    grads = torch.ops.aten._scaled_dot_product_flash_attention_backward.default(
+        mojo((1, 4, 96, 64)), q, k, v, res[0], res[1], None, None, res[4], res[5], 0.0, False, res[6], res[7])
+    kind, b = spy.calls[-1]
+    assert kind == "bwd" and tuple(b["dk"].shape) == (1, 2, 320, 64) and tuple(b["dq"].shape) == (1, 4, 96, 64)
+    assert [tuple(g.shape) for g in grads] == [(1, 4, 96, 64), (1, 2, 320, 64), (1, 2, 320, 64)]
 
 
 def test_contiguous_bhsd_goes_zero_copy_with_bhsd_output(host_backed_mojo):

@@ -138,7 +138,7 @@ const char* b200fa_strerror(int code) {
     case B200FA_ERR_BAD_STRIDE: return "tensor strides are unsupported (head_dim stride must be 1, others multiples of 16 bytes)";
     case B200FA_ERR_MISALIGNED: return "a tensor base address is not 16-byte aligned";
     case B200FA_ERR_WORKSPACE: return "workspace is missing, misaligned or too small";
-    case B200FA_ERR_UNSUPPORTED: return "configuration is not supported (head_dim must be 64 or 128, Sq == Sk, scale > 0, sm_100 device)";
+    case B200FA_ERR_UNSUPPORTED: return "configuration is not supported (head_dim must be 64 or 128, Sq == Sk when causal, scale > 0, sm_100 device)";
     case B200FA_ERR_CUDA: return "a CUDA runtime or driver call failed";
     case B200FA_ERR_NULL: return "a required pointer is null";
     case B200FA_ERR_TIMEOUT: return "a kernel gave up waiting on an internal barrier";
@@ -157,7 +157,8 @@ static int fwd_impl(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200
   if (B > 65535 || Hq > 65535 || Sq > (1 << 24)) return B200FA_ERR_BAD_SHAPE;
   if (D != 64 && D != 128) return B200FA_ERR_UNSUPPORTED;
   if (Hq % Hkv != 0) return B200FA_ERR_BAD_SHAPE;
-  if (Sq != Sk) return B200FA_ERR_UNSUPPORTED;
+  // a causal mask over Sq != Sk has two conventions (top-left, bottom-right); neither is offered
+  if (causal && Sq != Sk) return B200FA_ERR_UNSUPPORTED;
   if (!(scale > 0.f) || !std::isfinite(scale)) return B200FA_ERR_UNSUPPORTED;
   if (reinterpret_cast<uintptr_t>(lse) % 4 != 0) return B200FA_ERR_MISALIGNED;
   FwdParams p;
@@ -224,24 +225,24 @@ static int bwd_impl(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200
   if (!q || !k || !v || !out || !dout || !lse || !dq || !dk || !dv) return B200FA_ERR_NULL;
   if (dtype != kF32 && dtype != kBF16 && dtype != kF16) return B200FA_ERR_BAD_DTYPE;
   const int64_t B = q->shape[0], Hq = q->shape[1], S = q->shape[2], D = q->shape[3];
-  const int64_t Hkv = k->shape[1];
-  if (B <= 0 || Hq <= 0 || Hkv <= 0 || S <= 0) return B200FA_ERR_BAD_SHAPE;
-  if (B > 65535 || Hq > 65535 || S > (1 << 24)) return B200FA_ERR_BAD_SHAPE;
+  const int64_t Hkv = k->shape[1], Sk = k->shape[2];
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || S <= 0 || Sk <= 0) return B200FA_ERR_BAD_SHAPE;
+  if (B > 65535 || Hq > 65535 || S > (1 << 24) || Sk > (1 << 24)) return B200FA_ERR_BAD_SHAPE;
   if (D != 64 && D != 128) return B200FA_ERR_UNSUPPORTED;
   if (Hq % Hkv != 0) return B200FA_ERR_BAD_SHAPE;
-  if (k->shape[2] != S) return B200FA_ERR_UNSUPPORTED;
+  if (causal && Sk != S) return B200FA_ERR_UNSUPPORTED;
   if (!(scale > 0.f) || !std::isfinite(scale)) return B200FA_ERR_UNSUPPORTED;
   BwdParams p;
   std::memset(&p, 0, sizeof(p));
   int rc;
   if ((rc = check_view(q, B, Hq, S, D, dtype, &p.q)) != B200FA_OK) return rc;
-  if ((rc = check_view(k, B, Hkv, S, D, dtype, &p.k)) != B200FA_OK) return rc;
-  if ((rc = check_view(v, B, Hkv, S, D, dtype, &p.v)) != B200FA_OK) return rc;
+  if ((rc = check_view(k, B, Hkv, Sk, D, dtype, &p.k)) != B200FA_OK) return rc;
+  if ((rc = check_view(v, B, Hkv, Sk, D, dtype, &p.v)) != B200FA_OK) return rc;
   if ((rc = check_view(out, B, Hq, S, D, dtype, &p.out)) != B200FA_OK) return rc;
   if ((rc = check_view(dout, B, Hq, S, D, dtype, &p.dout)) != B200FA_OK) return rc;
   if ((rc = check_view(dq, B, Hq, S, D, dtype, &p.dq)) != B200FA_OK) return rc;
-  if ((rc = check_view(dk, B, Hkv, S, D, dtype, &p.dk)) != B200FA_OK) return rc;
-  if ((rc = check_view(dv, B, Hkv, S, D, dtype, &p.dv)) != B200FA_OK) return rc;
+  if ((rc = check_view(dk, B, Hkv, Sk, D, dtype, &p.dk)) != B200FA_OK) return rc;
+  if ((rc = check_view(dv, B, Hkv, Sk, D, dtype, &p.dv)) != B200FA_OK) return rc;
   const size_t need = b200fa_bwd_workspace_bytes(B, Hq, Hkv, S, D, dtype);
   if (!workspace || workspace_bytes < need || reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
     return B200FA_ERR_WORKSPACE;
@@ -252,7 +253,7 @@ static int bwd_impl(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200
   p.lse_log2 = reinterpret_cast<float*>(ws + align256(rows * 4));
   p.lse = lse;
   p.B = static_cast<int>(B); p.Hq = static_cast<int>(Hq); p.Hkv = static_cast<int>(Hkv);
-  p.S = static_cast<int>(S); p.Spad = static_cast<int>(spad); p.D = static_cast<int>(D);
+  p.S = static_cast<int>(S); p.Sk = static_cast<int>(Sk); p.Spad = static_cast<int>(spad); p.D = static_cast<int>(D);
   p.causal = causal ? 1 : 0;
   p.scale = scale;
   p.scale_log2 = scale * 1.4426950408889634f;

@@ -151,11 +151,12 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   // Block order: (batch, kv head) pairs are walked `sched_group` at a time, few enough that the
   // Q / dO rows they stream stay in L2, and inside such a group the K/V tiles with the most
   // causal work (the earliest) come first, so the last wave of CTAs is made of short ones.
-  const int m_tiles = (p.S + kTile - 1) / kTile;
+  const int m_tiles = (p.S + kTile - 1) / kTile;      // query tiles
+  const int n_tiles = (p.Sk + kTile - 1) / kTile;     // K/V tiles (== m_tiles when causal)
   int n_tile, hk, b;
   {
     const int pairs = p.B * p.Hkv;
-    const int per_group = sched_group * m_tiles;
+    const int per_group = sched_group * n_tiles;
     const int g = static_cast<int>(blockIdx.x) / per_group;
     const int gsize = min(sched_group, pairs - g * sched_group);
     const int within = static_cast<int>(blockIdx.x) - g * per_group;
@@ -308,7 +309,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     if (threadIdx.x == 0) CTA_CLOCK(2);
     {
       const int krow = n0 + j;
-      const bool valid = krow < p.S;
+      const bool valid = krow < p.Sk;
       constexpr int kHalf = kD / 4;
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
@@ -527,7 +528,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
   const int b = blockIdx.z;
   const int hk = h / (p.Hq / p.Hkv);
   const int m0 = m_tile * kTile;
-  const int n_tiles = kCausal ? (m_tile + 1) : m_tiles;
+  const int n_tiles = kCausal ? (m_tile + 1) : (p.Sk + kTile - 1) / kTile;
 
   if ((smem_u32(smem) & 1023u) != 0u) {
     if (threadIdx.x == 0 && p.status) atomicCAS(p.status, kStatusOk, 0x414c0001u);
@@ -873,7 +874,8 @@ cudaError_t launch_one(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  const int tiles = (p.S + kTile - 1) / kTile;
+  const int tiles = (p.S + kTile - 1) / kTile;        // query tiles: the dQ kernel's grid
+  const int kv_tiles = (p.Sk + kTile - 1) / kTile;    // K/V tiles: the dK/dV kernel's grid
   // fork: the dQ kernel goes to the side stream, behind everything enqueued so far.  Only
   // causal problems: their CTAs differ in length, which is what leaves a long partly idle tail;
   // with equal CTAs the tail is short and interleaving the two kernels only costs L2 hits.
@@ -891,7 +893,7 @@ cudaError_t launch_one(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
     const int64_t pairs = static_cast<int64_t>(p.B) * p.Hkv;
     if (sched_group < 1) sched_group = 1;
     if (sched_group > pairs) sched_group = pairs;
-    k1<<<static_cast<unsigned>(tiles * pairs), kDkdvThreads, Cfg::kSmemBytes, stream>>>(
+    k1<<<static_cast<unsigned>(kv_tiles * pairs), kDkdvThreads, Cfg::kSmemBytes, stream>>>(
         mq, mk, mv, mdo, p, static_cast<int>(sched_group));
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
@@ -915,8 +917,8 @@ cudaError_t launch_bwd_sm100(const BwdParams& p, int dtype, cudaStream_t stream,
   const bool bf16 = (dtype == kBF16);
   CUtensorMap mq, mk, mv, mdo;
   if (!encode_map_16bit(&mq, p.q, p.B, p.Hq, p.S, p.D, kTile, bf16)) return cudaErrorInvalidValue;
-  if (!encode_map_16bit(&mk, p.k, p.B, p.Hkv, p.S, p.D, kTile, bf16)) return cudaErrorInvalidValue;
-  if (!encode_map_16bit(&mv, p.v, p.B, p.Hkv, p.S, p.D, kTile, bf16)) return cudaErrorInvalidValue;
+  if (!encode_map_16bit(&mk, p.k, p.B, p.Hkv, p.Sk, p.D, kTile, bf16)) return cudaErrorInvalidValue;
+  if (!encode_map_16bit(&mv, p.v, p.B, p.Hkv, p.Sk, p.D, kTile, bf16)) return cudaErrorInvalidValue;
   if (!encode_map_16bit(&mdo, p.dout, p.B, p.Hq, p.S, p.D, kTile, bf16)) return cudaErrorInvalidValue;
   cudaError_t e;
 #define B200FA_DISPATCH(D_, BF_, C_) e = launch_one<D_, BF_, C_>(mq, mk, mv, mdo, p, stream)

@@ -28,7 +28,7 @@ struct BwdParams {
   const float* lse;  // (B, Hq, S) fp32 contiguous (natural log)
   float* dpsum;      // workspace: (B, Hq, Spad) rowsum(dO * O)
   float* lse_log2;   // workspace: (B, Hq, Spad) lse * log2(e)
-  int B, Hq, Hkv, S, Spad, D;
+  int B, Hq, Hkv, S, Sk, Spad, D;   // S: query rows (Spad: padded to 128); Sk: key rows (== S when causal)
   int causal;
   float scale;
   float scale_log2;

@@ -201,8 +201,8 @@ __global__ void __launch_bounds__(256) bwd_dkdv_simt_kernel(const BwdParams p) {
   const int group = p.Hq / p.Hkv;
   const float c = p.scale_log2;
 
-  stage_tile<T, kD>(sK, kD + 1, p.k, b, hk, n0, p.S);
-  stage_tile<T, kD>(sV, kD + 1, p.v, b, hk, n0, p.S);
+  stage_tile<T, kD>(sK, kD + 1, p.k, b, hk, n0, p.Sk);
+  stage_tile<T, kD>(sV, kD + 1, p.v, b, hk, n0, p.Sk);
   // thread owns key rows ty+16i and d columns tx+16k of dK/dV
   float dk[4][kD / 16], dv[4][kD / 16];
 #pragma unroll
@@ -258,7 +258,7 @@ __global__ void __launch_bounds__(256) bwd_dkdv_simt_kernel(const BwdParams p) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const int kc = n0 + tx + 16 * j;
-          const bool masked = (kc >= p.S) || (qr >= p.S) || (p.causal && kc > qr);
+          const bool masked = (kc >= p.Sk) || (qr >= p.S) || (p.causal && kc > qr);
           const float pv = masked ? 0.f : exp2f(s[i][j] * c - sLse[ql]);
           ds[i][j] = pv * (dp[i][j] - sDps[ql]);
           sP[ql * (kT + 1) + tx + 16 * j] = pv;
@@ -300,7 +300,7 @@ __global__ void __launch_bounds__(256) bwd_dkdv_simt_kernel(const BwdParams p) {
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int kr = n0 + ty + 16 * i;
-    if (kr < p.S) {
+    if (kr < p.Sk) {
       T* dkrow = row_ptr_mut<T>(p.dk, b, hk, kr);
       T* dvrow = row_ptr_mut<T>(p.dv, b, hk, kr);
 #pragma unroll
@@ -345,11 +345,11 @@ __global__ void __launch_bounds__(256) bwd_dq_simt_kernel(const BwdParams p) {
 #pragma unroll
     for (int k = 0; k < kD / 16; ++k) dq[i][k] = 0.f;
 
-  const int n_end = p.causal ? min(p.S, m0 + kT) : p.S;
+  const int n_end = p.causal ? min(p.Sk, m0 + kT) : p.Sk;
   for (int n0 = 0; n0 < n_end; n0 += kT) {
     __syncthreads();
-    stage_tile<T, kD>(sK, kD + 1, p.k, b, hk, n0, p.S);
-    stage_tile<T, kD>(sV, kD + 1, p.v, b, hk, n0, p.S);
+    stage_tile<T, kD>(sK, kD + 1, p.k, b, hk, n0, p.Sk);
+    stage_tile<T, kD>(sV, kD + 1, p.v, b, hk, n0, p.Sk);
     __syncthreads();
     float s[4][4], dp[4][4];
 #pragma unroll
@@ -383,7 +383,7 @@ __global__ void __launch_bounds__(256) bwd_dq_simt_kernel(const BwdParams p) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int kc = n0 + tx + 16 * j;
-        const bool masked = (kc >= p.S) || (qr >= p.S) || (p.causal && kc > qr);
+        const bool masked = (kc >= p.Sk) || (qr >= p.S) || (p.causal && kc > qr);
         const float pv = masked ? 0.f : exp2f(s[i][j] * c - lse2[i]);
         sP[ql * (kT + 1) + tx + 16 * j] = pv * (dp[i][j] - dps[i]);
       }
@@ -457,7 +457,8 @@ cudaError_t launch_bwd_t(const BwdParams& p, cudaStream_t stream) {
   e = cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return e;
   const int tiles = (p.S + kT - 1) / kT;
-  k1<<<dim3(tiles, p.Hkv, p.B), 256, smem, stream>>>(p);
+  const int kv_tiles = (p.Sk + kT - 1) / kT;
+  k1<<<dim3(kv_tiles, p.Hkv, p.B), 256, smem, stream>>>(p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   k2<<<dim3(tiles, p.Hq, p.B), 256, smem, stream>>>(p);

@@ -39,7 +39,10 @@ def flash_inputs(query, key, value, attn_mask=None, dropout_p=0.0, is_causal=Fal
     Metadata only — no device work.  Wider than the reference's gate
     (aten_fast.py:6971-7043, which needs causal, 16-bit, equal head counts and sm_90a):
     fp32/bf16/fp16, causal or not, ``Hq % Hkv == 0`` (needs ``enable_gqa`` when they differ),
-    ``Sq == Sk``, head_dim 64 or 128, no mask, no dropout, finite positive scale.
+    ``Sq == Sk`` when causal (a causal mask over ``Sq != Sk`` has a top-left and a bottom-right
+    convention - torch's CPU SDPA and the reference's kernels disagree - so neither is offered;
+    without a mask any ``Sq``, ``Sk`` pair is served), head_dim 64 or 128, no mask, no dropout,
+    finite positive scale.
     """
     q, k, v = payload(query), payload(key), payload(value)
     if q is None or k is None or v is None or attn_mask is not None:
@@ -56,9 +59,9 @@ def flash_inputs(query, key, value, attn_mask=None, dropout_p=0.0, is_causal=Fal
         return None
     batch, heads_q, seq_q, head_dim = q._shape
     kb, heads_kv, seq_k, kd = k._shape
-    if kb != batch or kd != head_dim or seq_q != seq_k:
+    if kb != batch or kd != head_dim or (is_causal and seq_q != seq_k):
         return None
-    if batch <= 0 or heads_q <= 0 or heads_kv <= 0 or seq_q <= 0 or head_dim not in (64, 128):
+    if batch <= 0 or heads_q <= 0 or heads_kv <= 0 or seq_q <= 0 or seq_k <= 0 or head_dim not in (64, 128):
         return None
     if heads_q % heads_kv != 0 or (heads_q != heads_kv and not enable_gqa):
         return None
@@ -157,7 +160,7 @@ def scaled_dot_product_flash_attention(query, key, value, dropout_p=0.0, is_caus
     if inputs is None:
         raise NotImplementedError(
             "aten::_scaled_dot_product_flash_attention on mojo needs fp32/bf16/fp16 (B,H,S,D) tensors with "
-            "head_dim 64 or 128, Sq == Sk, Hq % Hkv == 0 and a positive finite scale"
+            "head_dim 64 or 128, Sq == Sk when causal, Hq % Hkv == 0 and a positive finite scale"
         )
     q, k, v = inputs
     CALL_COUNTERS["aten::_scaled_dot_product_flash_attention"] += 1
@@ -207,8 +210,8 @@ def scaled_dot_product_flash_attention_backward(grad_out, query, key, value, out
         raise NotImplementedError("mojo flash attention backward: unsupported or payload-less arguments")
     q, k, v = inputs
     batch, heads_q, seq, head_dim = q._shape
-    if int(max_q) != seq or int(max_k) != seq:
-        raise NotImplementedError("mojo flash attention backward: max_q/max_k must equal the sequence length")
+    if int(max_q) != seq or int(max_k) != k._shape[2]:
+        raise NotImplementedError("mojo flash attention backward: max_q/max_k must equal the sequence lengths")
     if tuple(g._shape) != tuple(q._shape) or tuple(o._shape) != tuple(q._shape):
         raise RuntimeError("mojo flash attention backward: grad_out/out shape mismatch")
     if g._dtype != q._dtype or o._dtype != q._dtype:

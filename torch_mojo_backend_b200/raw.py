@@ -74,9 +74,9 @@ def flash_bwd(dout, q, k, v, out, lse, *, causal: bool, scale: float | None = No
     if dq is None:
         dq = torch.empty((B, Hq, S, D), dtype=q.dtype, device=q.device)
     if dk is None:
-        dk = torch.empty((B, Hkv, S, D), dtype=q.dtype, device=q.device)
+        dk = torch.empty(tuple(k.shape), dtype=q.dtype, device=q.device)
     if dv is None:
-        dv = torch.empty((B, Hkv, S, D), dtype=q.dtype, device=q.device)
+        dv = torch.empty(tuple(v.shape), dtype=q.dtype, device=q.device)
     code = dtype_code(q.dtype)
     need = _lib.bwd_workspace_bytes(B, Hq, Hkv, S, D, code)
     if workspace is None:

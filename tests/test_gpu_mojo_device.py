@@ -54,6 +54,26 @@ def test_direct_flash_op_returns_a_real_logsumexp(mojo):
     assert_within("lse", res[1].cpu(), exp["lse"], TOL_LSE)
 
 
+def test_cross_attention_through_sdpa_with_grad(mojo):
+    """A short query over a longer key sequence, no mask, GQA, through the SDPA router and the
+    generated autograd node: gradients come back at the key length and head count."""
+    g = torch.Generator().manual_seed(13)
+    q = (torch.randn(2, 8, 200, 128, generator=g) * 0.5).bfloat16()
+    k = (torch.randn(2, 2, 777, 128, generator=g) * 0.5).bfloat16()
+    v = (torch.randn(2, 2, 777, 128, generator=g) * 0.5).bfloat16()
+    dout = torch.randn(2, 8, 200, 128, generator=g).bfloat16()
+    ref_out, rdq, rdk, rdv = O.sdpa_backward(q, k, v, dout, False, 128 ** -0.5)
+    qm, km, vm = (t.to(mojo).requires_grad_() for t in (q, k, v))
+    out = torch.nn.functional.scaled_dot_product_attention(qm, km, vm, enable_gqa=True)
+    out.backward(dout.to(mojo))
+    assert_within("out", out.detach().cpu(), ref_out, TOL_16BIT, torch.bfloat16)
+    assert tuple(km.grad.shape) == (2, 2, 777, 128)
+    for name, got, ref in (("dq", qm.grad, rdq), ("dk", km.grad, rdk), ("dv", vm.grad, rdv)):
+        assert_within(name, got.cpu(), ref, TOL_16BIT, torch.bfloat16)
+    with pytest.raises(NotImplementedError):
+        torch.nn.functional.scaled_dot_product_attention(qm, km, vm, is_causal=True, enable_gqa=True)
+
+
 def test_autocast_block_runs_the_bf16_kernel(mojo):
     g = torch.Generator().manual_seed(11)
     q, k, v = (torch.randn(2, 4, 256, 64, generator=g) * 0.5 for _ in range(3))

@@ -86,7 +86,8 @@ size_t b200fa_bwd_workspace_bytes(int64_t batch, int64_t heads_q, int64_t heads_
                                   int64_t head_dim, int dtype);
 
 /*
- * Backward: given dout and the forward's out/lse, writes dq (B,Hq,S,D) and dk, dv (B,Hkv,S,D).
+ * Backward: given dout and the forward's out/lse, writes dq (B,Hq,Sq,D) and dk, dv (B,Hkv,Sk,D);
+ * `seqlen` of b200fa_bwd_workspace_bytes is Sq.
  * `workspace` is caller-owned device scratch of at least b200fa_bwd_workspace_bytes(...)
  * bytes, 256-byte aligned; its contents on entry are irrelevant (the library clears what it
  * needs on `stream`).

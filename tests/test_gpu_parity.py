@@ -122,6 +122,43 @@ def test_unmasked_attention_over_another_key_length(dtype, B, Hq, Hkv, Sq, Sk, D
         assert_within("simt dq", s_dq, rdq, tol, dtype)
 
 
+def test_randomised_shapes_agree_with_the_exact_fp32_kernels():
+    """A seeded sweep over ragged lengths, GQA groups, head dims, dtypes, masks and (when
+    unmasked) unequal key lengths: the tensor-core kernels against the exact-fp32 SIMT kernels
+    on the same device buffers, status word clean, no NaN."""
+    import random
+
+    rng = random.Random(20260902)
+    gen = torch.Generator(device="cuda").manual_seed(7)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lengths = [1, 17, 64, 127, 128, 129, 255, 256, 300, 511, 640, 1000, 1537]
+    for _ in range(120):
+        D = rng.choice([64, 128])
+        dtype = rng.choice([torch.bfloat16, torch.float16])
+        Hkv, group, B = rng.choice([1, 2, 3]), rng.choice([1, 1, 2, 4]), rng.choice([1, 2])
+        causal = rng.random() < 0.6
+        Sq = rng.choice(lengths + [rng.randint(1, 1800)])
+        Sk = Sq if causal else rng.choice([Sq, Sq, rng.randint(1, 1800), 128, 1])
+        q = (torch.randn(B, Hkv * group, Sq, D, device="cuda", generator=gen) * 0.5).to(dtype)
+        k = (torch.randn(B, Hkv, Sk, D, device="cuda", generator=gen) * 0.5).to(dtype)
+        v = (torch.randn(B, Hkv, Sk, D, device="cuda", generator=gen) * 0.5).to(dtype)
+        do = torch.randn(B, Hkv * group, Sq, D, device="cuda", generator=gen).to(dtype)
+        status.zero_()
+        out, lse = raw.flash_fwd(q, k, v, causal=causal, status=status)
+        grads = raw.flash_bwd(do, q, k, v, out, lse, causal=causal, status=status)
+        s_out, s_lse = raw.flash_fwd(q, k, v, causal=causal, simt=True)
+        s_grads = raw.flash_bwd(do, q, k, v, s_out, s_lse, causal=causal, simt=True)
+        torch.cuda.synchronize()
+        what = f"{dtype} B{B} Hq{Hkv * group} Hkv{Hkv} Sq{Sq} Sk{Sk} D{D} causal={causal}"
+        assert int(status.item()) == 0, what
+        assert (lse - s_lse).abs().max().item() < TOL_LSE, what
+        for name, got, ref in zip(("out", "dq", "dk", "dv"), (out,) + tuple(grads), (s_out,) + tuple(s_grads)):
+            assert not torch.isnan(got.float()).any().item(), what
+            # both sides are rounded to 16 bits: allow the tolerance plus one ulp of the larger values
+            bound = TOL_16BIT + 2.0 ** -7 * ref.float().abs().max().item()
+            assert (got.float() - ref.float()).abs().max().item() < bound, f"{name}: {what}"
+
+
 def test_causal_mask_over_unequal_lengths_is_refused():
     q = torch.zeros(1, 2, 128, 64, dtype=torch.bfloat16, device="cuda")
     k = torch.zeros(1, 2, 256, 64, dtype=torch.bfloat16, device="cuda")

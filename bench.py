@@ -351,13 +351,20 @@ def run_e2e(cfg, rank, world, local, args):
     flash_fwd = torch.ops.aten._scaled_dot_product_flash_attention
     flash_bwd = torch.ops.aten._scaled_dot_product_flash_attention_backward
 
-    # pieces: every batch entry, its kv heads in `split` groups (a GQA group is never cut); each
-    # piece is a contiguous block of the host buffers
-    split = 2 if cfg.Hkv % 2 == 0 else 1
+    # pieces: contiguous blocks of the host buffers, about 40 MB of upload each (smaller ones
+    # cost more in host-side dispatch than the overlap wins) - ranges of batch entries, or, when
+    # a single batch entry is larger than that, its kv heads in two groups (never cutting a GQA
+    # group)
     rep_q = cfg.Hq // cfg.Hkv
-    pieces = [(i, (slice(g * cfg.Hkv // split * rep_q, (g + 1) * cfg.Hkv // split * rep_q),
-                   slice(g * cfg.Hkv // split, (g + 1) * cfg.Hkv // split)))
-              for i in range(cfg.B) for g in range(split)]
+    wanted = max(1, min(2 * cfg.B, h2d // (40 << 20)))
+    if wanted <= cfg.B:
+        bounds = [round(n * cfg.B / wanted) for n in range(wanted + 1)]
+        pieces = [(slice(a, b), (slice(None), slice(None))) for a, b in zip(bounds, bounds[1:]) if b > a]
+    else:
+        split = 2 if cfg.Hkv % 2 == 0 else 1
+        pieces = [(slice(i, i + 1), (slice(g * cfg.Hkv // split * rep_q, (g + 1) * cfg.Hkv // split * rep_q),
+                                     slice(g * cfg.Hkv // split, (g + 1) * cfg.Hkv // split)))
+                  for i in range(cfg.B) for g in range(split)]
 
     def step_pipelined(keep):
         """`keep` collects every device tensor of the step: the three streams use one another's
@@ -366,10 +373,10 @@ def run_e2e(cfg, rank, world, local, args):
             s.wait_stream(main)
         for i, (qs, ks) in pieces:
             with torch.cuda.stream(s_in):
-                dq_in = [hq[i:i + 1, qs].to(dev, non_blocking=True), hk[i:i + 1, ks].to(dev, non_blocking=True),
-                         hv[i:i + 1, ks].to(dev, non_blocking=True)]
+                dq_in = [hq[i, qs].to(dev, non_blocking=True), hk[i, ks].to(dev, non_blocking=True),
+                         hv[i, ks].to(dev, non_blocking=True)]
                 if cfg.backward:
-                    dq_in.append(hdo[i:i + 1, qs].to(dev, non_blocking=True))
+                    dq_in.append(hdo[i, qs].to(dev, non_blocking=True))
                 uploaded = torch.cuda.Event()
                 uploaded.record(s_in)
             with torch.cuda.stream(s_run):
@@ -384,9 +391,9 @@ def run_e2e(cfg, rank, world, local, args):
                 computed.record(s_run)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(computed)
-                res_out[i:i + 1, qs].copy_(out, non_blocking=True)
+                res_out[i, qs].copy_(out, non_blocking=True)
                 for dst, g, hs in zip(res_grads, grads, (qs, ks, ks)):
-                    dst[i:i + 1, hs].copy_(g, non_blocking=True)
+                    dst[i, hs].copy_(g, non_blocking=True)
             keep.extend(dq_in)
             keep.extend((out, lse) + tuple(grads))
         for s in (s_in, s_run, s_out):
@@ -428,14 +435,18 @@ def run_e2e(cfg, rank, world, local, args):
 
     ms_pipe = time_steps(pipelined_and_release)
     tf = lambda ms: round(world * flops / (ms * 1e-3) / 1e12, 2)
-    return {"value": tf(ms_pipe), "unit": "TFLOP/s", "ms_per_step": round(ms_pipe, 3), "steps": steps,
-            "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-            "api": "aten::_scaled_dot_product_flash_attention + _backward on mojo tensors, the batch in "
-                   f"{len(pieces)} (batch entry, kv-head group) pieces; uploads, kernels and downloads on three "
-                   "streams; pinned host in, pinned host out",
-            "matches_single_call_bitwise": bool(same),
-            "single_call": {"value": tf(ms_single), "ms_per_step": round(ms_single, 3),
-                            "api": "F.scaled_dot_product_attention + backward over the whole batch, one stream"}}
+    pipelined = {"value": tf(ms_pipe), "ms_per_step": round(ms_pipe, 3), "pieces": len(pieces),
+                 "matches_single_call_bitwise": bool(same),
+                 "api": "aten::_scaled_dot_product_flash_attention + _backward on mojo tensors, the batch in "
+                        f"{len(pieces)} contiguous pieces; uploads, kernels and downloads on three streams"}
+    single = {"value": tf(ms_single), "ms_per_step": round(ms_single, 3),
+              "api": "F.scaled_dot_product_attention + backward over the whole batch, one stream"}
+    # both are the public operator API with pinned host buffers in and out; the headline is the
+    # faster way of driving it for this workload (small steps do not repay the pipelining)
+    best_ms, mode = (ms_pipe, "pipelined") if ms_pipe <= ms_single else (ms_single, "single_call")
+    return {"value": tf(best_ms), "unit": "TFLOP/s", "ms_per_step": round(best_ms, 3), "steps": steps,
+            "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "mode": mode,
+            "pipelined": pipelined, "single_call": single}
 
 
 def run_reference(args):

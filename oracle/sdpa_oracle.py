@@ -123,21 +123,32 @@ def sdpa_backward(q, k, v, dout, causal: bool, scale: float):
     return out.detach(), q32.grad, k32.grad, v32.grad
 
 
-def time_cpu(cfg: Config, *, backward: bool, sample_heads: int, reps: int = 1, threads: int | None = None):
-    """Time the CPU path on a (B=1, `sample_heads` KV-head groups) slice of `cfg` in its real dtype.
+def time_cpu(cfg: Config, *, backward: bool, sample_heads: int = 0, reps: int = 1, threads: int | None = None,
+             sample_flops: float = 2.0e12, target_seconds: float = 0.0):
+    """Time the CPU path on a bounded slice of `cfg` in its real dtype.
 
-    Returns (TFLOP/s, seconds per rep, threads used, description of the sample).
+    The slice is whole (batch entry, KV-head group) units: `sample_heads` KV-head groups of one
+    batch entry when given, otherwise as many units as bring one repetition to about
+    `sample_flops` (KV-head groups of one batch entry first, then further batch entries).  It is
+    repeated `reps` times, and beyond that until `target_seconds` of CPU work have been spent
+    (at most 20 repetitions); the best repetition counts.
+
+    Returns (TFLOP/s, seconds of the best repetition, threads used, description of the sample).
     """
     threads = threads or os.cpu_count() or 1
     torch.set_num_threads(threads)
     group = cfg.Hq // cfg.Hkv
-    hkv = max(1, min(sample_heads, cfg.Hkv))
-    q, k, v, dout = make_inputs(cfg, B=1, Hq=hkv * group, Hkv=hkv)
-    flops = 4.0 * 1 * hkv * group * cfg.S * cfg.S * cfg.D * (0.5 if cfg.causal else 1.0)
-    if backward:
-        flops *= 3.5  # forward + backward, the way a training step runs it
-    best = float("inf")
-    for _ in range(max(1, reps)):
+    unit = 4.0 * group * cfg.S * cfg.S * cfg.D * (0.5 if cfg.causal else 1.0) * (3.5 if backward else 1.0)
+    if sample_heads > 0:
+        hkv, batch = max(1, min(sample_heads, cfg.Hkv)), 1
+    else:
+        units = max(1, int(round(sample_flops / unit)))
+        hkv = min(cfg.Hkv, units)
+        batch = max(1, min(cfg.B, units // hkv))
+    q, k, v, dout = make_inputs(cfg, B=batch, Hq=hkv * group, Hkv=hkv)
+    flops = unit * hkv * batch   # forward, plus 2.5x forward for the backward: the way a training step runs it
+    best, spent, done = float("inf"), 0.0, 0
+    while done < max(1, reps) or (spent < target_seconds and done < 20):
         t0 = time.perf_counter()
         if backward:
             qq, kk, vv = (t.clone().requires_grad_() for t in (q, k, v))
@@ -147,6 +158,8 @@ def time_cpu(cfg: Config, *, backward: bool, sample_heads: int, reps: int = 1, t
             o.backward(dout)
         else:
             torch.ops.aten._scaled_dot_product_flash_attention_for_cpu(q, k, v, 0.0, cfg.causal, scale=cfg.scale)
-        best = min(best, time.perf_counter() - t0)
-    sample = f"B=1, Hq={hkv * group}, Hkv={hkv}, S={cfg.S}, D={cfg.D}, {'fwd+bwd' if backward else 'fwd'}, best of {reps}"
+        dt = time.perf_counter() - t0
+        best, spent, done = min(best, dt), spent + dt, done + 1
+    sample = (f"B={batch}, Hq={hkv * group}, Hkv={hkv}, S={cfg.S}, D={cfg.D}, {'fwd+bwd' if backward else 'fwd'}, "
+              f"best of {done} ({spent:.1f} s of CPU work)")
     return flops / best / 1e12, best, threads, sample

@@ -492,7 +492,7 @@ template <int kD, bool kBf16, bool kCausal>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
               const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
-              const BwdParams p) {
+              const __grid_constant__ CUtensorMap mapDQ, const BwdParams p) {
   using Cfg = BwdCfg<kD>;
   constexpr int kTmemS = 0, kTmemDP = 256, kTmemDQ = 384;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -513,6 +513,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
   uint64_t* dp_full = s_full + 2;                  // dP ready
   uint64_t* ds_full = dp_full + 1;                 // dS written, dP consumed (8 warp arrivals)
   uint64_t* acc_full = ds_full + 1;                // dQ complete
+  uint64_t* staged = acc_full + 1;                 // dQ tile staged in shared memory (8 warp arrivals)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::kNumBars);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -549,6 +550,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
     mbar_init(dp_full, 1);
     mbar_init(ds_full, 8);
     mbar_init(acc_full, 1);
+    mbar_init(staged, 8);
     *abort_flag = 0;
     fence_mbar_init();
     fence_proxy_async_smem();
@@ -630,19 +632,37 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
     tc_fence_after();
     if (threadIdx.x == 0) CTA_CLOCK(2);
     {
-      const int qrow = m0 + r;
-      const bool valid = qrow < p.S;
+      // The scaled 16-bit dQ tile is staged in the Q buffer (every MMA that read it has
+      // completed) in the swizzled box layout and leaves through TMA stores: whole 128-byte
+      // lines, rows past the end of the sequence clipped by the tensor map, and nothing for
+      // the CTA to wait on but the read of shared memory.
       constexpr int kHalf = kD / 2;
-      uint16_t* dst = reinterpret_cast<uint16_t*>(p.dq.ptr) +
-                      (static_cast<int64_t>(b) * p.dq.sb + static_cast<int64_t>(h) * p.dq.sh +
-                       static_cast<int64_t>(qrow) * p.dq.ss) + wg * kHalf;
       const uint32_t tacc = tmem_base + lane_off + kTmemDQ + wg * kHalf;
 #pragma unroll
       for (int ch = 0; ch < kHalf / 32; ++ch) {
         uint32_t a[32];
         tmem_ld32(tacc + ch * 32, a);
         tmem_wait_ld();
-        if (valid) store_row_16bit<kBf16>(dst + ch * 32, reinterpret_cast<const float*>(a), p.scale);
+        const float* af = reinterpret_cast<const float*>(a);
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          uint4 w;
+          w.x = pack2<kBf16>(af[v * 8 + 0] * p.scale, af[v * 8 + 1] * p.scale);
+          w.y = pack2<kBf16>(af[v * 8 + 2] * p.scale, af[v * 8 + 3] * p.scale);
+          w.z = pack2<kBf16>(af[v * 8 + 4] * p.scale, af[v * 8 + 5] * p.scale);
+          w.w = pack2<kBf16>(af[v * 8 + 6] * p.scale, af[v * 8 + 7] * p.scale);
+          const int chunk = (wg * kHalf + ch * 32) / 8 + v;   // 16-byte chunk of the row
+          *reinterpret_cast<uint4*>(sQ + (chunk >> 3) * kSubTileBytes + r * 128 + (((chunk & 7) ^ (r & 7)) << 4)) = w;
+        }
+      }
+      fence_proxy_async_smem();
+      mbar_arrive_warp(staged);
+      if (threadIdx.x == 0) {
+        B200FA_WAIT(staged, 0, 0x921);
+#pragma unroll
+        for (int cs = 0; cs < Cfg::kSub; ++cs) tma_store_4d(&mapDQ, sQ + cs * kSubTileBytes, cs * 64, m0, h, b);
+        tma_store_commit();
+        tma_store_wait_read();
       }
     }
   } else if (warp == 8 || warp == 9) {
@@ -851,7 +871,7 @@ SideStream* side_stream_for(int dev) {
 
 template <int kD, bool kBf16, bool kCausal>
 cudaError_t launch_one(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mdo,
-                       const BwdParams& p, cudaStream_t stream) {
+                       const CUtensorMap& mdq, const BwdParams& p, cudaStream_t stream) {
   using Cfg = BwdCfg<kD>;
   cudaError_t e = cudaSuccess;
   if (p.parts & 1) {
@@ -899,7 +919,7 @@ cudaError_t launch_one(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
     if (e != cudaSuccess) return e;
   }
   if (p.parts & 4) {
-    k2<<<dim3(tiles, p.Hq, p.B), kThreads, Cfg::kSmemBytes, side ? side->stream : stream>>>(mq, mk, mv, mdo, p);
+    k2<<<dim3(tiles, p.Hq, p.B), kThreads, Cfg::kSmemBytes, side ? side->stream : stream>>>(mq, mk, mv, mdo, mdq, p);
     e = cudaGetLastError();
   }
   if (side) {
@@ -915,13 +935,14 @@ cudaError_t launch_one(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
 
 cudaError_t launch_bwd_sm100(const BwdParams& p, int dtype, cudaStream_t stream, int* launches) {
   const bool bf16 = (dtype == kBF16);
-  CUtensorMap mq, mk, mv, mdo;
+  CUtensorMap mq, mk, mv, mdo, mdq;
   if (!encode_map_16bit(&mq, p.q, p.B, p.Hq, p.S, p.D, kTile, bf16)) return cudaErrorInvalidValue;
   if (!encode_map_16bit(&mk, p.k, p.B, p.Hkv, p.Sk, p.D, kTile, bf16)) return cudaErrorInvalidValue;
   if (!encode_map_16bit(&mv, p.v, p.B, p.Hkv, p.Sk, p.D, kTile, bf16)) return cudaErrorInvalidValue;
   if (!encode_map_16bit(&mdo, p.dout, p.B, p.Hq, p.S, p.D, kTile, bf16)) return cudaErrorInvalidValue;
+  if (!encode_map_16bit(&mdq, p.dq, p.B, p.Hq, p.S, p.D, kTile, bf16)) return cudaErrorInvalidValue;
   cudaError_t e;
-#define B200FA_DISPATCH(D_, BF_, C_) e = launch_one<D_, BF_, C_>(mq, mk, mv, mdo, p, stream)
+#define B200FA_DISPATCH(D_, BF_, C_) e = launch_one<D_, BF_, C_>(mq, mk, mv, mdo, mdq, p, stream)
   if (p.D == 128) {
     if (bf16) { if (p.causal) B200FA_DISPATCH(128, true, true); else B200FA_DISPATCH(128, true, false); }
     else      { if (p.causal) B200FA_DISPATCH(128, false, true); else B200FA_DISPATCH(128, false, false); }

@@ -75,32 +75,6 @@ struct BwdCfg {
       (kOffBars > kOffDqBars ? kOffBars : kOffDqBars) + kNumBars * 8 + 16;
 };
 
-template <bool kBf16>
-__device__ __forceinline__ void store_row_16bit(uint16_t* dst, const float* v, float mul) {
-#pragma unroll
-  for (int g = 0; g < 4; ++g) {
-    uint4 w;
-    w.x = pack2<kBf16>(v[g * 8 + 0] * mul, v[g * 8 + 1] * mul);
-    w.y = pack2<kBf16>(v[g * 8 + 2] * mul, v[g * 8 + 3] * mul);
-    w.z = pack2<kBf16>(v[g * 8 + 4] * mul, v[g * 8 + 5] * mul);
-    w.w = pack2<kBf16>(v[g * 8 + 6] * mul, v[g * 8 + 7] * mul);
-    *reinterpret_cast<uint4*>(dst + g * 8) = w;
-  }
-}
-
-template <bool kBf16>
-__device__ __forceinline__ void store_half_row_16bit(uint16_t* dst, const float* v, float mul) {
-#pragma unroll
-  for (int g = 0; g < 2; ++g) {
-    uint4 w;
-    w.x = pack2<kBf16>(v[g * 8 + 0] * mul, v[g * 8 + 1] * mul);
-    w.y = pack2<kBf16>(v[g * 8 + 2] * mul, v[g * 8 + 3] * mul);
-    w.z = pack2<kBf16>(v[g * 8 + 4] * mul, v[g * 8 + 5] * mul);
-    w.w = pack2<kBf16>(v[g * 8 + 6] * mul, v[g * 8 + 7] * mul);
-    *reinterpret_cast<uint4*>(dst + g * 8) = w;
-  }
-}
-
 #define B200FA_WAIT(bar, parity, site) \
   if (!mbar_wait((bar), (parity), abort_flag, p.status, (site))) goto teardown
 
@@ -115,6 +89,7 @@ template <int kD, bool kBf16, bool kCausal>
 __global__ void __launch_bounds__(kDkdvThreads, 1)
 bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                 const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
+                const __grid_constant__ CUtensorMap mapDK, const __grid_constant__ CUtensorMap mapDV,
                 const BwdParams p, const int sched_group) {
   using Cfg = BwdCfg<kD>;
   // TMEM: two 128-column work buffers (step i uses buffer i & 1 for S^T, then dP^T, then dS^T),
@@ -139,6 +114,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   uint64_t* acc_full = ds_full + 1;                // dK, dV complete
   uint64_t* s_free = acc_full + 1;                 // S^T read into registers (8 warp arrivals)
   uint64_t* p_empty = s_free + 1;                  // dV MMA has consumed the P^T tile
+  uint64_t* staged = p_empty + 1;                  // dV and dK tiles staged in shared memory (16 warp arrivals)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::kNumBars);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -193,6 +169,7 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     mbar_init(acc_full, 2);        // both MMA-issuing lanes
     mbar_init(s_free, 16);
     mbar_init(p_empty, 1);
+    mbar_init(staged, 16);
     *abort_flag = 0;
     fence_mbar_init();
     fence_proxy_async_smem();
@@ -308,28 +285,41 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     tc_fence_after();
     if (threadIdx.x == 0) CTA_CLOCK(2);
     {
-      const int krow = n0 + j;
-      const bool valid = krow < p.Sk;
-      constexpr int kHalf = kD / 4;
+      // The 16-bit dV and dK tiles are staged in the Q / dO ring (every MMA that read it has
+      // completed) in the swizzled box layout and leave through TMA stores: whole 128-byte
+      // lines, key rows past the end of the sequence clipped by the tensor map.
+      constexpr int kQuarter = kD / 4;
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
-        const View4& dst_view = which == 0 ? p.dv : p.dk;
-        uint16_t* dst = reinterpret_cast<uint16_t*>(dst_view.ptr) +
-                        (static_cast<int64_t>(b) * dst_view.sb + static_cast<int64_t>(hk) * dst_view.sh +
-                         static_cast<int64_t>(krow) * dst_view.ss) + wg * kHalf;
-        const uint32_t tacc = tmem_base + lane_off + (which == 0 ? kTmemDV : kTmemDK) + wg * kHalf;
+        uint8_t* stage = sQ + which * Cfg::kTileBytes;
+        const uint32_t tacc = tmem_base + lane_off + (which == 0 ? kTmemDV : kTmemDK) + wg * kQuarter;
         const float mul = which == 0 ? 1.f : p.scale;
-        if constexpr (kHalf == 32) {
-          uint32_t a[32];
-          tmem_ld32(tacc, a);
-          tmem_wait_ld();
-          if (valid) store_row_16bit<kBf16>(dst, reinterpret_cast<const float*>(a), mul);
-        } else {
-          uint32_t a[16];
-          tmem_ld16(tacc, a);
-          tmem_wait_ld();
-          if (valid) store_half_row_16bit<kBf16>(dst, reinterpret_cast<const float*>(a), mul);
+        uint32_t a[kQuarter];
+        if constexpr (kQuarter == 32) tmem_ld32(tacc, a); else tmem_ld16(tacc, a);
+        tmem_wait_ld();
+        const float* af = reinterpret_cast<const float*>(a);
+#pragma unroll
+        for (int v = 0; v < kQuarter / 8; ++v) {
+          uint4 w;
+          w.x = pack2<kBf16>(af[v * 8 + 0] * mul, af[v * 8 + 1] * mul);
+          w.y = pack2<kBf16>(af[v * 8 + 2] * mul, af[v * 8 + 3] * mul);
+          w.z = pack2<kBf16>(af[v * 8 + 4] * mul, af[v * 8 + 5] * mul);
+          w.w = pack2<kBf16>(af[v * 8 + 6] * mul, af[v * 8 + 7] * mul);
+          const int chunk = wg * (kQuarter / 8) + v;   // 16-byte chunk of the row
+          *reinterpret_cast<uint4*>(stage + (chunk >> 3) * kSubTileBytes + j * 128 + (((chunk & 7) ^ (j & 7)) << 4)) = w;
         }
+      }
+      fence_proxy_async_smem();
+      mbar_arrive_warp(staged);
+      if (threadIdx.x == 0) {
+        B200FA_WAIT(staged, 0, 0x521);
+#pragma unroll
+        for (int cs = 0; cs < Cfg::kSub; ++cs) {
+          tma_store_4d(&mapDV, sQ + cs * kSubTileBytes, cs * 64, n0, hk, b);
+          tma_store_4d(&mapDK, sQ + Cfg::kTileBytes + cs * kSubTileBytes, cs * 64, n0, hk, b);
+        }
+        tma_store_commit();
+        tma_store_wait_read();
       }
     }
   } else if (warp >= 16 && warp <= 18) {
@@ -871,7 +861,8 @@ SideStream* side_stream_for(int dev) {
 
 template <int kD, bool kBf16, bool kCausal>
 cudaError_t launch_one(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mdo,
-                       const CUtensorMap& mdq, const BwdParams& p, cudaStream_t stream) {
+                       const CUtensorMap& mdq, const CUtensorMap& mdk, const CUtensorMap& mdv, const BwdParams& p,
+                       cudaStream_t stream) {
   using Cfg = BwdCfg<kD>;
   cudaError_t e = cudaSuccess;
   if (p.parts & 1) {
@@ -914,7 +905,7 @@ cudaError_t launch_one(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
     if (sched_group < 1) sched_group = 1;
     if (sched_group > pairs) sched_group = pairs;
     k1<<<static_cast<unsigned>(kv_tiles * pairs), kDkdvThreads, Cfg::kSmemBytes, stream>>>(
-        mq, mk, mv, mdo, p, static_cast<int>(sched_group));
+        mq, mk, mv, mdo, mdk, mdv, p, static_cast<int>(sched_group));
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }
@@ -935,14 +926,16 @@ cudaError_t launch_one(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
 
 cudaError_t launch_bwd_sm100(const BwdParams& p, int dtype, cudaStream_t stream, int* launches) {
   const bool bf16 = (dtype == kBF16);
-  CUtensorMap mq, mk, mv, mdo, mdq;
+  CUtensorMap mq, mk, mv, mdo, mdq, mdk, mdv;
   if (!encode_map_16bit(&mq, p.q, p.B, p.Hq, p.S, p.D, kTile, bf16)) return cudaErrorInvalidValue;
   if (!encode_map_16bit(&mk, p.k, p.B, p.Hkv, p.Sk, p.D, kTile, bf16)) return cudaErrorInvalidValue;
   if (!encode_map_16bit(&mv, p.v, p.B, p.Hkv, p.Sk, p.D, kTile, bf16)) return cudaErrorInvalidValue;
   if (!encode_map_16bit(&mdo, p.dout, p.B, p.Hq, p.S, p.D, kTile, bf16)) return cudaErrorInvalidValue;
   if (!encode_map_16bit(&mdq, p.dq, p.B, p.Hq, p.S, p.D, kTile, bf16)) return cudaErrorInvalidValue;
+  if (!encode_map_16bit(&mdk, p.dk, p.B, p.Hkv, p.Sk, p.D, kTile, bf16)) return cudaErrorInvalidValue;
+  if (!encode_map_16bit(&mdv, p.dv, p.B, p.Hkv, p.Sk, p.D, kTile, bf16)) return cudaErrorInvalidValue;
   cudaError_t e;
-#define B200FA_DISPATCH(D_, BF_, C_) e = launch_one<D_, BF_, C_>(mq, mk, mv, mdo, mdq, p, stream)
+#define B200FA_DISPATCH(D_, BF_, C_) e = launch_one<D_, BF_, C_>(mq, mk, mv, mdo, mdq, mdk, mdv, p, stream)
   if (p.D == 128) {
     if (bf16) { if (p.causal) B200FA_DISPATCH(128, true, true); else B200FA_DISPATCH(128, true, false); }
     else      { if (p.causal) B200FA_DISPATCH(128, false, true); else B200FA_DISPATCH(128, false, false); }

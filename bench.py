@@ -39,7 +39,7 @@ NOMINAL_BF16_TFLOPS = 2250.0
 FALLBACK_BF16_TFLOPS = 1590.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the backward dK/dV kernel on the
 # C3 workload, from the ncu capture summarised in profiles/bwd_dkdv_kernel_C3.md.
-BWD_DKDV_DRAM_TRAFFIC_BYTES = 394.4e6
+BWD_DKDV_DRAM_TRAFFIC_BYTES = 395.2e6
 
 
 def load_peaks():

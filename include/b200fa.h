@@ -34,7 +34,7 @@
 extern "C" {
 #endif
 
-#define B200FA_VERSION 1
+#define B200FA_VERSION 2
 
 /* element types */
 #define B200FA_F32 0
@@ -53,6 +53,17 @@ extern "C" {
 #define B200FA_ERR_NULL (-8)
 #define B200FA_ERR_TIMEOUT (-9)
 
+/* causal argument of every entry point: query row i sees key column j iff
+ *   B200FA_CAUSAL_NONE          always
+ *   B200FA_CAUSAL_TOP_LEFT      j <= i                 (torch's is_causal on the CPU / math SDPA paths)
+ *   B200FA_CAUSAL_BOTTOM_RIGHT  j <= i + (Sk - Sq)     (the reference kernels' convention,
+ *                               torch_mojo_backend/eager_flash_attention/fa4_fwd_kernel.mojo:266-273)
+ * The two coincide when Sq == Sk.  A query row that sees no key at all (possible when
+ * Sq > Sk under the bottom-right rule) gets out = 0, lse = -inf and zero gradients. */
+#define B200FA_CAUSAL_NONE 0
+#define B200FA_CAUSAL_TOP_LEFT 1
+#define B200FA_CAUSAL_BOTTOM_RIGHT 2
+
 /* A 4-D tensor view in logical (batch, head, sequence, head_dim) order; strides in elements. */
 typedef struct b200fa_tensor4 {
   void* ptr;
@@ -64,9 +75,8 @@ typedef struct b200fa_tensor4 {
  * Forward: out = softmax(scale * q k^T [+ causal mask]) v,  lse = logsumexp of the scaled,
  * masked scores (natural log), fp32, contiguous (B, Hq, Sq).
  *   q, out : (B, Hq, Sq, D);  k, v : (B, Hkv, Sk, D) with Hq % Hkv == 0 (query head h reads
- *   key/value head h / (Hq / Hkv));  D in {64, 128};  Sq == Sk when causal (a causal mask over
- *   Sq != Sk has a top-left and a bottom-right convention, neither is offered), any Sq, Sk
- *   otherwise, which the reference's gate does not serve (aten_fast.py:7029-7030).
+ *   key/value head h / (Hq / Hkv));  D in {64, 128};  any Sq, Sk, masked or not (the reference's
+ *   gate needs Sq == Sk, aten_fast.py:7029-7030); `causal` is one of B200FA_CAUSAL_*.
  *   dtype  : B200FA_BF16 / B200FA_F16 run the tcgen05 tensor-core kernel,
  *            B200FA_F32 runs an exact-fp32 SIMT kernel.
  * Replaces flash_attention_fwd_<dtype>_d<D>_causal{,_strided_qkv,_bhsd}
@@ -104,6 +114,55 @@ int b200fa_bwd(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_te
                const b200fa_tensor4* dq, const b200fa_tensor4* dk, const b200fa_tensor4* dv,
                void* workspace, size_t workspace_bytes, int dtype, int causal, float scale,
                void* stream, int device, uint32_t* status_word);
+
+/*
+ * Forward and backward with dropout on the attention probabilities.  Element (b, h, i, j) is
+ * kept when its byte of a Philox4x32-10 stream keyed by (philox_seed, philox_offset) is
+ * >= b200fa_dropout_threshold(dropout_p) = round(256 p) (at most 255): the drop probability is
+ * quantised to threshold/256 and kept probabilities are scaled by 256/(256 - threshold).  The
+ * logsumexp is that of the undropped scores.  Counter layout: key = seed; counter =
+ * (j / 16, i, low and high word of philox_offset + b*Hq + h); byte 4*w + r of the call (word w,
+ * byte r from the low end) belongs to column 16*(j/16) + 4*w + r.  One forward consumes B*Hq
+ * consecutive offsets; the backward must be given the same (dropout_p, seed, offset).
+ * `exact_fp32` != 0 runs the exact-fp32 SIMT kernels (cross-checks).  dropout_p == 0 is
+ * b200fa_fwd / b200fa_bwd.  The reference reserves the (seed, offset) pair on the host
+ * (torch_mojo_backend/mojo_device/torch_mojo_device_module.py:84-99) and returns placeholder
+ * slots for it (torch_mojo_backend/eager_kernels/aten_fast.py:7726-7734); no reference kernel
+ * consumes it.
+ */
+int b200fa_fwd_dropout(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_tensor4* v,
+                       const b200fa_tensor4* out, float* lse, int dtype, int causal, float scale,
+                       float dropout_p, uint64_t philox_seed, uint64_t philox_offset, int exact_fp32,
+                       void* stream, int device, uint32_t* status_word);
+int b200fa_bwd_dropout(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_tensor4* v,
+                       const b200fa_tensor4* out, const b200fa_tensor4* dout, const float* lse,
+                       const b200fa_tensor4* dq, const b200fa_tensor4* dk, const b200fa_tensor4* dv,
+                       void* workspace, size_t workspace_bytes, int dtype, int causal, float scale,
+                       float dropout_p, uint64_t philox_seed, uint64_t philox_offset, int exact_fp32,
+                       void* stream, int device, uint32_t* status_word);
+uint32_t b200fa_dropout_threshold(float dropout_p);
+/* Host-side evaluation of the same stream: the 16 bytes of key columns [16*col_block,
+ * 16*col_block + 16) of query row `row` of head `batch_head` = b*Hq + h (tests; no device work). */
+void b200fa_dropout_bytes_host(uint64_t philox_seed, uint64_t philox_offset, int64_t batch_head, int64_t row,
+                               int64_t col_block, uint8_t* out16);
+
+/*
+ * Forward for short query blocks against a long key/value sequence (decode): the key sequence
+ * is split over many thread blocks, each streams its share of K and V once for every query
+ * head of the GQA group and every query row, and a second kernel merges the partial softmax
+ * results.  Needs (Hq / Hkv) * Sq <= B200FA_SPLITKV_MAX_ROWS; any dtype; same out / lse
+ * contract as b200fa_fwd.  `workspace`: b200fa_fwd_splitkv_workspace_bytes(...) bytes of
+ * caller-owned device scratch, 256-byte aligned (fp32 partial outputs and (max, sum) pairs per
+ * split).  Takes the place of the reference's single-kernel decode path
+ * (torch_mojo_backend/eager_kernels/aten_fast.py:9171-9203: q_len == 1, kv_len <= 4096).
+ */
+#define B200FA_SPLITKV_MAX_ROWS 16
+size_t b200fa_fwd_splitkv_workspace_bytes(int64_t batch, int64_t heads_q, int64_t heads_kv, int64_t seqlen_q,
+                                          int64_t seqlen_k, int64_t head_dim);
+int b200fa_fwd_splitkv(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_tensor4* v,
+                       const b200fa_tensor4* out, float* lse, void* workspace, size_t workspace_bytes,
+                       int dtype, int causal, float scale, void* stream, int device,
+                       uint32_t* status_word);
 
 /*
  * b200fa_bwd for callers that cannot allocate device memory.  (No counterpart in the
@@ -166,6 +225,21 @@ int b200fa_bwd_parts(const b200fa_tensor4* q, const b200fa_tensor4* k, const b20
                      const b200fa_tensor4* dq, const b200fa_tensor4* dk, const b200fa_tensor4* dv,
                      void* workspace, size_t workspace_bytes, int dtype, int causal, float scale,
                      void* stream, int device, uint32_t* status_word, int parts);
+
+/*
+ * Bounded waits.  Every wait inside the tensor-core kernels gives up after a budget of SM
+ * cycles (default about 2 s; environment variable B200FA_WAIT_BUDGET, or this setter; 0 restores
+ * the default), writes 0x5741xxxx (xxxx = where it gave up) to the status word and lets the
+ * kernel finish; later thread blocks that see a non-zero status word leave at once.
+ * b200fa_status_to_error maps a status word read back from the device to B200FA_OK or
+ * B200FA_ERR_TIMEOUT.  b200fa_selftest_wait_timeout launches a one-warp kernel whose only job
+ * is to wait `budget_cycles` on a barrier nobody arrives at, so the give-up path can be tested
+ * without disturbing an attention kernel.  No counterpart in the reference.
+ */
+void b200fa_set_wait_budget(long long cycles);
+long long b200fa_wait_budget(void);
+int b200fa_status_to_error(uint32_t status_value);
+int b200fa_selftest_wait_timeout(uint32_t* status_word, long long budget_cycles, void* stream, int device);
 
 /* Human-readable text for a B200FA_ERR_* code (static storage). */
 const char* b200fa_strerror(int code);

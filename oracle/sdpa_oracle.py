@@ -104,23 +104,67 @@ def make_inputs(cfg: Config, seed: int = 0, B: int | None = None, Hq: int | None
     return q, k, v, dout
 
 
-def sdpa_forward(q, k, v, causal: bool, scale: float):
-    """(out fp32, lse fp32) from torch's CPU flash op on fp32 upcasts."""
+def _bottom_right_mask(sq: int, sk: int) -> torch.Tensor:
+    """Boolean (sq, sk) mask of the bottom-right aligned causal rule ``j <= i + (sk - sq)``
+    (torch_mojo_backend/eager_flash_attention/fa4_fwd_kernel.mojo:266-273)."""
+    return torch.arange(sk)[None, :] <= torch.arange(sq)[:, None] + (sk - sq)
+
+
+def sdpa_forward(q, k, v, causal, scale: float):
+    """(out fp32, lse fp32) from torch's CPU flash op on fp32 upcasts.  ``causal``: False/0,
+    True/1 (torch's is_causal: top-left aligned) or 2 (bottom-right aligned, given to torch as
+    an explicit boolean mask; needs every query row to see at least one key, i.e. Sk >= Sq)."""
     q32, k32, v32 = (t.detach().float().contiguous() for t in (q, k, v))
+    if int(causal) == 2:
+        # the CPU flash op takes an additive mask of the query dtype
+        mask = torch.zeros(q.shape[2], k.shape[2]).masked_fill(~_bottom_right_mask(q.shape[2], k.shape[2]), float("-inf"))
+        out, lse = torch.ops.aten._scaled_dot_product_flash_attention_for_cpu(
+            q32, k32, v32, 0.0, False, attn_mask=mask, scale=scale
+        )
+        return out, lse
     out, lse = torch.ops.aten._scaled_dot_product_flash_attention_for_cpu(
-        q32, k32, v32, 0.0, causal, scale=scale
+        q32, k32, v32, 0.0, bool(causal), scale=scale
     )
     return out, lse
 
 
-def sdpa_backward(q, k, v, dout, causal: bool, scale: float):
-    """(out, dq, dk, dv) in fp32 via autograd through CPU SDPA on fp32 upcasts."""
+def sdpa_backward(q, k, v, dout, causal, scale: float):
+    """(out, dq, dk, dv) in fp32 via autograd through CPU SDPA on fp32 upcasts (``causal`` as in
+    sdpa_forward)."""
     q32, k32, v32 = (t.detach().float().contiguous().requires_grad_() for t in (q, k, v))
-    out = torch.nn.functional.scaled_dot_product_attention(
-        q32, k32, v32, dropout_p=0.0, is_causal=causal, scale=scale, enable_gqa=q.shape[1] != k.shape[1]
-    )
+    gqa = q.shape[1] != k.shape[1]
+    if int(causal) == 2:
+        out = torch.nn.functional.scaled_dot_product_attention(
+            q32, k32, v32, attn_mask=_bottom_right_mask(q.shape[2], k.shape[2]), dropout_p=0.0, scale=scale,
+            enable_gqa=gqa)
+    else:
+        out = torch.nn.functional.scaled_dot_product_attention(
+            q32, k32, v32, dropout_p=0.0, is_causal=bool(causal), scale=scale, enable_gqa=gqa)
     out.backward(dout.detach().float())
     return out.detach(), q32.grad, k32.grad, v32.grad
+
+
+def sdpa_dropout(q, k, v, dout, causal, scale: float, keep: torch.Tensor, keep_scale: float):
+    """(out, lse, dq, dk, dv) in fp32 for attention with a GIVEN dropout mask, from plain torch CPU
+    ops and autograd: softmax of the masked scaled scores, entries multiplied by
+    ``keep * keep_scale`` before they meet V.  ``keep``: bool (B, Hq, Sq, Sk).  torch's own SDPA
+    cannot be handed a mask of ours, so this is the torch-side oracle for the dropout path; the
+    float64 restatement (oracle/restatement.py) is checked against it."""
+    q32, k32, v32 = (t.detach().float().contiguous().requires_grad_() for t in (q, k, v))
+    group = q.shape[1] // k.shape[1]
+    kk = k32.repeat_interleave(group, dim=1) if group > 1 else k32
+    vv = v32.repeat_interleave(group, dim=1) if group > 1 else v32
+    s = torch.matmul(q32, kk.transpose(-1, -2)) * scale
+    sq, sk = s.shape[-2:]
+    mode = int(causal)
+    if mode:
+        off = 0 if mode == 1 else sk - sq
+        s = s.masked_fill(~(torch.arange(sk)[None, :] <= torch.arange(sq)[:, None] + off), float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)
+    p = torch.softmax(s, dim=-1)
+    out = torch.matmul(p * (keep.float() * keep_scale), vv)
+    out.backward(dout.detach().float())
+    return out.detach(), lse.detach(), q32.grad, k32.grad, v32.grad
 
 
 def time_cpu(cfg: Config, *, backward: bool, sample_heads: int = 0, reps: int = 1, threads: int | None = None,

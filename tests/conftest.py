@@ -36,16 +36,26 @@ class BridgeSpy:
     def __init__(self):
         self.calls = []
 
-    def fwd(self, q, k, v, out, lse_ptr, dtype, causal, scale, stream, device, status_ptr=0, *, simt=False):
+    def fwd(self, q, k, v, out, lse_ptr, dtype, causal, scale, stream, device, status_ptr=0, *, simt=False,
+            dropout=None):
         self.calls.append(("fwd", dict(q=q, k=k, v=v, out=out, lse_ptr=lse_ptr, dtype=dtype, causal=causal,
-                                       scale=scale, stream=stream, device=device)))
+                                       scale=scale, stream=stream, device=device, status_ptr=status_ptr,
+                                       dropout=dropout)))
         return 0
 
     def bwd(self, q, k, v, out, dout, lse_ptr, dq, dk, dv, workspace_ptr, workspace_bytes, dtype, causal, scale,
-            stream, device, status_ptr=0, *, simt=False, parts=7):
+            stream, device, status_ptr=0, *, simt=False, parts=7, dropout=None):
         self.calls.append(("bwd", dict(q=q, k=k, v=v, out=out, dout=dout, lse_ptr=lse_ptr, dq=dq, dk=dk, dv=dv,
                                        workspace_ptr=workspace_ptr, workspace_bytes=workspace_bytes, dtype=dtype,
-                                       causal=causal, scale=scale, stream=stream, device=device)))
+                                       causal=causal, scale=scale, stream=stream, device=device,
+                                       status_ptr=status_ptr, dropout=dropout)))
+        return 0
+
+    def fwd_splitkv(self, q, k, v, out, lse_ptr, workspace_ptr, workspace_bytes, dtype, causal, scale, stream,
+                    device, status_ptr=0):
+        self.calls.append(("fwd_splitkv", dict(q=q, k=k, v=v, out=out, lse_ptr=lse_ptr, workspace_ptr=workspace_ptr,
+                                               workspace_bytes=workspace_bytes, dtype=dtype, causal=causal,
+                                               scale=scale, stream=stream, device=device)))
         return 0
 
 
@@ -68,5 +78,9 @@ def host_backed_mojo(mojo_registered, monkeypatch):
     monkeypatch.setattr(flash_ops, "_stream_for", lambda index: 0)
     monkeypatch.setattr(_lib, "fwd", spy.fwd)
     monkeypatch.setattr(_lib, "bwd", spy.bwd)
+    monkeypatch.setattr(_lib, "fwd_splitkv", spy.fwd_splitkv)
+    # the per-device status word lives in (redirected) host memory for the duration of the test
+    monkeypatch.setattr(flash_ops, "_status_words", {})
+    spy.status_ptr = flash_ops._status_ptr(0)
     spy.allocations = allocations
     return spy

@@ -28,7 +28,7 @@ def test_library_exports_every_declared_symbol():
     lib = _lib.load()
     for name in declared_symbols():
         assert hasattr(lib, name), name
-    assert _lib.version() == 1
+    assert _lib.version() == 2
     assert _lib.launch_count() == 0 or _lib.launch_count() > 0
 
 
@@ -67,7 +67,13 @@ FAKE = 0x7F0000000000  # never dereferenced: validation rejects the call first
         (dict(dtype=7), _lib.ERR_BAD_DTYPE),
         (dict(q_shape=(1, 2, 128, 96)), _lib.ERR_UNSUPPORTED),  # head_dim not 64/128
         (dict(k_shape=(1, 3, 128, 64), q_shape=(1, 4, 128, 64)), _lib.ERR_BAD_SHAPE),  # Hq % Hkv
-        (dict(k_shape=(1, 2, 256, 64)), _lib.ERR_UNSUPPORTED),  # Sq != Sk under a causal mask
+        (dict(causal=3), _lib.ERR_UNSUPPORTED),  # not one of B200FA_CAUSAL_*
+        (dict(q_stride=(0, 8192, 64, 1), q_shape=(2, 2, 128, 64), k_shape=(2, 2, 128, 64)), _lib.ERR_BAD_STRIDE),  # broadcast batch
+        (dict(k_stride=(16384, 0, 64, 1)), _lib.ERR_BAD_STRIDE),  # broadcast heads
+        (dict(out_stride=(16384, 64, 64, 1)), _lib.ERR_BAD_STRIDE),  # output heads overlap one another
+        (dict(dropout=(1.0, 1, 0)), _lib.ERR_UNSUPPORTED),
+        (dict(dropout=(-0.5, 1, 0)), _lib.ERR_UNSUPPORTED),
+        (dict(q_shape=(65535, 65535, 128, 64), k_shape=(65535, 65535, 128, 64)), _lib.ERR_BAD_SHAPE),  # grid index overflow
         (dict(scale=0.0), _lib.ERR_UNSUPPORTED),
         (dict(scale=float("nan")), _lib.ERR_UNSUPPORTED),
         (dict(q_stride=(16384, 8192, 64, 2)), _lib.ERR_BAD_STRIDE),  # head_dim stride must be 1
@@ -83,12 +89,12 @@ def test_forward_validates_before_launch(mutate, expected):
     k_shape = mutate.get("k_shape", (1, 2, 128, 64))
     v_shape = mutate.get("v_shape", k_shape)
     q = _t4(mutate.get("q_ptr", FAKE), q_shape, mutate.get("q_stride"))
-    k = _t4(FAKE + 0x100000, k_shape)
+    k = _t4(FAKE + 0x100000, k_shape, mutate.get("k_stride"))
     v = _t4(FAKE + 0x200000, v_shape)
-    out = _t4(FAKE + 0x300000, q_shape)
+    out = _t4(FAKE + 0x300000, q_shape, mutate.get("out_stride"))
     before = _lib.launch_count()
-    rc = _lib.fwd(q, k, v, out, mutate.get("lse", FAKE + 0x400000), mutate.get("dtype", _lib.BF16), True,
-                  mutate.get("scale", 0.125), 0, 0)
+    rc = _lib.fwd(q, k, v, out, mutate.get("lse", FAKE + 0x400000), mutate.get("dtype", _lib.BF16),
+                  mutate.get("causal", True), mutate.get("scale", 0.125), 0, 0, dropout=mutate.get("dropout"))
     assert rc == expected, _lib.strerror(rc)
     assert _lib.launch_count() == before
 
@@ -101,6 +107,44 @@ def test_backward_rejects_small_or_missing_workspace():
         rc = _lib.bwd(t[0], t[1], t[2], t[3], t[4], FAKE + 0xA00000, t[5], t[6], t[7], ws_ptr, ws_bytes, _lib.BF16,
                       True, 0.125, 0, 0)
         assert rc == _lib.ERR_WORKSPACE
+
+
+def test_split_kv_entry_point_validates_before_launch():
+    q = _t4(FAKE, (1, 8, 1, 128))
+    k = _t4(FAKE + 0x100000, (1, 2, 4096, 128))
+    out = _t4(FAKE + 0x300000, (1, 8, 1, 128))
+    need = _lib.fwd_splitkv_workspace_bytes(1, 8, 2, 1, 4096, 128)
+    assert need > 0 and need % 256 == 0
+    before = _lib.launch_count()
+    assert _lib.fwd_splitkv(q, k, k, out, FAKE + 0x400000, 0, need, _lib.BF16, False, 0.1, 0, 0) == _lib.ERR_WORKSPACE
+    assert _lib.fwd_splitkv(q, k, k, out, FAKE + 0x400000, FAKE + 0x500000, need - 1, _lib.BF16, False, 0.1, 0,
+                            0) == _lib.ERR_WORKSPACE
+    # 8 query rows x 4 heads per kv head = 32 rows: more than one split-KV thread block carries
+    q32 = _t4(FAKE, (1, 8, 8, 128))
+    assert _lib.fwd_splitkv(q32, k, k, _t4(FAKE + 0x300000, (1, 8, 8, 128)), FAKE + 0x400000, FAKE + 0x500000,
+                            1 << 30, _lib.BF16, False, 0.1, 0, 0) == _lib.ERR_UNSUPPORTED
+    assert _lib.launch_count() == before
+
+
+def test_wait_budget_and_status_helpers():
+    default = _lib.wait_budget()
+    assert default > 0
+    _lib.set_wait_budget(12345)
+    assert _lib.wait_budget() == 12345
+    _lib.set_wait_budget(0)   # back to the default (or B200FA_WAIT_BUDGET)
+    assert _lib.wait_budget() == default
+    assert _lib.status_to_error(0) == _lib.OK
+    assert _lib.status_to_error(0x57410100) == _lib.ERR_TIMEOUT
+    assert _lib.status_to_error(0x414C0000) == _lib.ERR_CUDA
+    # the self-test kernel is refused without a status word or with a silly budget, before any launch
+    before = _lib.launch_count()
+    assert _lib.selftest_wait_timeout(0, 1000, 0, 0) == _lib.ERR_NULL
+    assert _lib.selftest_wait_timeout(FAKE, 0, 0, 0) == _lib.ERR_UNSUPPORTED
+    assert _lib.launch_count() == before
+
+
+def test_dropout_threshold_quantises_to_256ths():
+    assert [_lib.dropout_threshold(p) for p in (0.0, 0.001, 0.1, 0.25, 0.5, 0.999)] == [0, 0, 26, 64, 128, 255]
 
 
 def test_valid_call_without_gpu_reports_cuda_error_not_success():

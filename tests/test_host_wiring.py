@@ -36,7 +36,8 @@ def test_ineligible_regimes_never_reach_the_bridge(host_backed_mojo):
     q = mojo((1, 2, 128, 64))
     bad = [
         dict(attn_mask=torch.ones(128, 128, dtype=torch.bool).to("mojo")),
-        dict(dropout_p=0.1),
+        dict(dropout_p=1.0),
+        dict(dropout_p=-0.1),
         dict(scale=-1.0),
         dict(scale=float("inf")),
     ]
@@ -46,9 +47,6 @@ def test_ineligible_regimes_never_reach_the_bridge(host_backed_mojo):
     with pytest.raises(NotImplementedError):  # head_dim 96
         x = mojo((1, 2, 128, 96))
         torch.nn.functional.scaled_dot_product_attention(x, x, x, is_causal=True)
-    with pytest.raises(NotImplementedError):  # Sq != Sk under a causal mask: two conventions, none served
-        torch.nn.functional.scaled_dot_product_attention(q, mojo((1, 2, 64, 64)), mojo((1, 2, 64, 64)),
-                                                         is_causal=True)
     with pytest.raises(NotImplementedError):  # GQA shapes without enable_gqa
         torch.nn.functional.scaled_dot_product_attention(mojo((1, 4, 128, 64)), q, q, is_causal=True)
     with pytest.raises(NotImplementedError):  # mixed dtypes
@@ -82,6 +80,76 @@ def test_cross_attention_lengths_reach_the_bridge_when_unmasked(host_backed_mojo
     kind, b = spy.calls[-1]
     assert kind == "bwd" and tuple(b["dk"].shape) == (1, 2, 320, 64) and tuple(b["dq"].shape) == (1, 4, 96, 64)
     assert [tuple(g.shape) for g in grads] == [(1, 4, 96, 64), (1, 2, 320, 64), (1, 2, 320, 64)]
+
+
+def test_causal_over_unequal_lengths_keeps_torchs_top_left_rule(host_backed_mojo):
+    """is_causal over Sq != Sk reaches the library as causal=True, which _lib maps to
+    B200FA_CAUSAL_TOP_LEFT: the convention of torch's own SDPA, not the reference kernels'
+    bottom-right one (that one is only reachable through the C ABI)."""
+    spy = host_backed_mojo
+    q, k = mojo((1, 2, 128, 64)), mojo((1, 2, 320, 64))
+    torch.nn.functional.scaled_dot_product_attention(q, k, k, is_causal=True)
+    kind, a = spy.calls[-1]
+    assert kind == "fwd" and a["causal"] is True and _lib.causal_code(a["causal"]) == _lib.CAUSAL_TOP_LEFT
+    assert tuple(a["k"].shape) == (1, 2, 320, 64)
+
+
+def test_decode_shaped_forward_goes_to_the_split_kv_entry_point(host_backed_mojo):
+    spy = host_backed_mojo
+    q, k = mojo((2, 8, 1, 128)), mojo((2, 2, 4096, 128))
+    before = flash_ops.CALL_COUNTERS["forward_split_kv"]
+    res = torch.ops.aten._scaled_dot_product_flash_attention.default(q, k, k, 0.0, False, False)
+    kind, a = spy.calls[-1]
+    assert kind == "fwd_splitkv" and flash_ops.CALL_COUNTERS["forward_split_kv"] == before + 1
+    assert a["workspace_bytes"] == _lib.fwd_splitkv_workspace_bytes(2, 8, 2, 1, 4096, 128) > 0
+    assert tuple(res[0].shape) == (2, 8, 1, 128) and tuple(res[1].shape) == (2, 8, 1)
+    # too many query rows for one split-KV thread block, or a short key sequence: the prefill kernel
+    torch.ops.aten._scaled_dot_product_flash_attention.default(mojo((2, 8, 8, 128)), k, k, 0.0, False, False)
+    assert spy.calls[-1][0] == "fwd"
+    torch.ops.aten._scaled_dot_product_flash_attention.default(q, mojo((2, 2, 256, 128)), mojo((2, 2, 256, 128)),
+                                                               0.0, False, False)
+    assert spy.calls[-1][0] == "fwd"
+
+
+def test_dropout_reserves_philox_state_and_the_backward_repeats_it(host_backed_mojo):
+    spy = host_backed_mojo
+    torch.mojo.manual_seed_all(1234)
+    q = mojo((2, 4, 128, 64)).requires_grad_()
+    k = mojo((2, 4, 128, 64)).requires_grad_()
+    out = torch.nn.functional.scaled_dot_product_attention(q, k, k, dropout_p=0.25, is_causal=True)
+    kind, a = spy.calls[-1]
+    assert kind == "fwd" and a["dropout"] == (0.25, 1234, 0)
+    # the generator advanced by one counter value per (batch, head)
+    assert torch.mojo._reserve_philox_state(0, 0) == (1234, 8)
+    out2 = torch.nn.functional.scaled_dot_product_attention(q, k, k, dropout_p=0.25, is_causal=True)
+    assert spy.calls[-1][1]["dropout"] == (0.25, 1234, 8)
+    out.backward(mojo((2, 4, 128, 64)))
+    kind, b = spy.calls[-1]
+    assert kind == "bwd" and b["dropout"] == (0.25, 1234, 0)   # the first call's pair, not the generator's current one
+    # the aten tuple carries the pair: on the device (uint64[2]) and as a host-side copy
+    res = torch.ops.aten._scaled_dot_product_flash_attention.default(q.detach(), k.detach(), k.detach(), 0.5, False, False)
+    assert res[6]._philox == (1234, 16) and res[6].cpu().tolist() == [1234, 16]
+    assert res[6].detach()._philox == (1234, 16)
+    # without dropout nothing is reserved and the library gets no dropout argument
+    torch.ops.aten._scaled_dot_product_flash_attention.default(q.detach(), k.detach(), k.detach(), 0.0, False, False)
+    assert spy.calls[-1][1]["dropout"] is None and torch.mojo._reserve_philox_state(0, 0) == (1234, 24)
+
+
+def test_every_call_passes_the_device_status_word_and_check_status_raises(host_backed_mojo):
+    spy = host_backed_mojo
+    q = mojo((1, 2, 128, 64))
+    res = torch.ops.aten._scaled_dot_product_flash_attention.default(q, q, q, 0.0, True, False)
+    assert spy.calls[-1][1]["status_ptr"] == spy.status_ptr != 0
+    torch.ops.aten._scaled_dot_product_flash_attention_backward.default(
+        q, q, q, q, res[0], res[1], None, None, 128, 128, 0.0, True, res[6], res[7])
+    assert spy.calls[-1][1]["status_ptr"] == spy.status_ptr
+    flash_ops.check_status(0)   # clean
+    # what a kernel that gave up on a wait leaves behind
+    flash_ops._status_words[0]._cuda_view().fill_(0x57410320)
+    with pytest.raises(_lib.B200FAError) as err:
+        flash_ops.check_status(0)
+    assert err.value.code == _lib.ERR_TIMEOUT and "0x57410320" in str(err.value)
+    flash_ops.check_status(0)   # cleared by the failed check
 
 
 def test_contiguous_bhsd_goes_zero_copy_with_bhsd_output(host_backed_mojo):
@@ -213,9 +281,30 @@ def test_backward_makes_logsumexp_contiguous_and_checks_arguments(host_backed_mo
     with pytest.raises(NotImplementedError):
         torch.ops.aten._scaled_dot_product_flash_attention_backward.default(
             out, q, q, q, out, lse, None, None, 64, 128, 0.0, True, rng, off)
-    with pytest.raises(RuntimeError):
-        torch.ops.aten._scaled_dot_product_flash_attention_backward.default(
-            out, q, q, q, out, torch.zeros(1, 2, 64).to("mojo"), None, None, 128, 128, 0.0, True, rng, off)
+
+
+def test_backward_recomputes_the_forward_when_out_or_logsumexp_is_unusable(host_backed_mojo):
+    """The reference recomputes the forward when the saved out / logsumexp come back without
+    their payload (aten_fast.py:7805-7818) instead of raising inside the autograd engine."""
+    spy = host_backed_mojo
+    q = mojo((1, 2, 128, 64))
+    out = mojo((1, 2, 128, 64))
+    rng = torch.zeros(2, dtype=torch.uint64).to("mojo")
+    off = torch.zeros((), dtype=torch.uint64).to("mojo")
+    before = flash_ops.CALL_COUNTERS["backward_recomputed_forward"]
+    n = len(spy.calls)
+    for bad_out, bad_lse in ((out, torch.zeros(1, 2, 64).to("mojo")),          # wrong logsumexp shape
+                             (out, torch.zeros(1, 2, 128)),                     # a CPU tensor: no payload
+                             (torch.zeros(1, 2, 128, 64), torch.zeros(1, 2, 128).to("mojo"))):
+        grads = torch.ops.aten._scaled_dot_product_flash_attention_backward.default(
+            out, q, q, q, bad_out, bad_lse, None, None, 128, 128, 0.0, True, rng, off)
+        assert [tuple(g.shape) for g in grads] == [(1, 2, 128, 64)] * 3
+    kinds = [c[0] for c in spy.calls[n:]]
+    assert kinds == ["fwd", "bwd"] * 3
+    assert flash_ops.CALL_COUNTERS["backward_recomputed_forward"] == before + 3
+    # the recomputed out / lse are what the backward kernel reads
+    assert spy.calls[-1][1]["out"].ptr == spy.calls[-2][1]["out"].ptr
+    assert spy.calls[-1][1]["lse_ptr"] == spy.calls[-2][1]["lse_ptr"]
 
 
 def test_gqa_gradients_come_back_at_kv_head_count(host_backed_mojo):
@@ -265,5 +354,7 @@ def test_host_code_has_no_sync_and_no_cpu_math_path():
     tests/test_fa4_host_wiring.py:1107-1112) and must not import the test oracle."""
     import inspect
 
-    src = inspect.getsource(flash_ops)
-    assert "synchronize" not in src and "oracle" not in src and ".cpu()" not in src
+    assert "oracle" not in inspect.getsource(flash_ops)
+    for fn in (flash_ops.flash_forward, flash_ops.flash_backward, flash_ops.scaled_dot_product_flash_attention):
+        src = inspect.getsource(fn)
+        assert "synchronize" not in src and ".cpu()" not in src and ".item()" not in src, fn.__name__

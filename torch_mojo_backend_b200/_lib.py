@@ -14,10 +14,11 @@ import os
 from typing import Sequence
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-# B200FA_LIB overrides the library path (used to try experimental builds)
-LIB_PATH = os.environ.get("B200FA_LIB") or os.path.join(_HERE, "libb200fa.so")
+LIB_PATH = os.path.join(_HERE, "libb200fa.so")
 
 F32, BF16, F16 = 0, 1, 2
+CAUSAL_NONE, CAUSAL_TOP_LEFT, CAUSAL_BOTTOM_RIGHT = 0, 1, 2
+SPLITKV_MAX_ROWS = 16
 
 OK = 0
 ERR_BAD_DTYPE = -1
@@ -40,6 +41,16 @@ EXPORTED_SYMBOLS = (
     "b200fa_bwd_parts",
     "b200fa_bwd_no_alloc",
     "b200fa_no_alloc_scratch_bytes",
+    "b200fa_fwd_dropout",
+    "b200fa_bwd_dropout",
+    "b200fa_dropout_threshold",
+    "b200fa_dropout_bytes_host",
+    "b200fa_fwd_splitkv_workspace_bytes",
+    "b200fa_fwd_splitkv",
+    "b200fa_set_wait_budget",
+    "b200fa_wait_budget",
+    "b200fa_status_to_error",
+    "b200fa_selftest_wait_timeout",
     "b200fa_strerror",
     "b200fa_last_error_detail",
     "b200fa_version",
@@ -104,6 +115,30 @@ def load() -> ctypes.CDLL:
     lib.b200fa_no_alloc_scratch_bytes.restype = ctypes.c_size_t
     lib.b200fa_bwd_parts.argtypes = bwd_args + [ctypes.c_int]
     lib.b200fa_bwd_parts.restype = ctypes.c_int
+    drop_args = [ctypes.c_float, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_int]
+    lib.b200fa_fwd_dropout.argtypes = fwd_args[:8] + drop_args + fwd_args[8:]
+    lib.b200fa_fwd_dropout.restype = ctypes.c_int
+    lib.b200fa_bwd_dropout.argtypes = bwd_args[:14] + drop_args + bwd_args[14:]
+    lib.b200fa_bwd_dropout.restype = ctypes.c_int
+    lib.b200fa_dropout_threshold.argtypes = [ctypes.c_float]
+    lib.b200fa_dropout_threshold.restype = ctypes.c_uint32
+    lib.b200fa_dropout_bytes_host.argtypes = [ctypes.c_uint64, ctypes.c_uint64, ctypes.c_int64, ctypes.c_int64,
+                                              ctypes.c_int64, ctypes.c_void_p]
+    lib.b200fa_dropout_bytes_host.restype = None
+    lib.b200fa_fwd_splitkv_workspace_bytes.argtypes = [ctypes.c_int64] * 6
+    lib.b200fa_fwd_splitkv_workspace_bytes.restype = ctypes.c_size_t
+    lib.b200fa_fwd_splitkv.argtypes = [t4p, t4p, t4p, t4p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t,
+                                       ctypes.c_int, ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_int,
+                                       ctypes.c_void_p]
+    lib.b200fa_fwd_splitkv.restype = ctypes.c_int
+    lib.b200fa_set_wait_budget.argtypes = [ctypes.c_longlong]
+    lib.b200fa_set_wait_budget.restype = None
+    lib.b200fa_wait_budget.argtypes = []
+    lib.b200fa_wait_budget.restype = ctypes.c_longlong
+    lib.b200fa_status_to_error.argtypes = [ctypes.c_uint32]
+    lib.b200fa_status_to_error.restype = ctypes.c_int
+    lib.b200fa_selftest_wait_timeout.argtypes = [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_int]
+    lib.b200fa_selftest_wait_timeout.restype = ctypes.c_int
     lib.b200fa_bwd_workspace_bytes.argtypes = [ctypes.c_int64] * 5 + [ctypes.c_int]
     lib.b200fa_bwd_workspace_bytes.restype = ctypes.c_size_t
     lib.b200fa_strerror.argtypes = [ctypes.c_int]
@@ -134,32 +169,89 @@ def bwd_workspace_bytes(B: int, Hq: int, Hkv: int, S: int, D: int, dtype: int) -
     return int(load().b200fa_bwd_workspace_bytes(B, Hq, Hkv, S, D, dtype))
 
 
-def fwd(q: Tensor4, k: Tensor4, v: Tensor4, out: Tensor4, lse_ptr: int, dtype: int, causal: bool,
-        scale: float, stream: int, device: int, status_ptr: int = 0, *, simt: bool = False) -> int:
-    """Raw forward call; returns the library's status code."""
+def causal_code(causal) -> int:
+    """bool or B200FA_CAUSAL_* -> the integer the library takes (True = top-left, torch's rule)."""
+    return int(causal)
+
+
+def fwd(q: Tensor4, k: Tensor4, v: Tensor4, out: Tensor4, lse_ptr: int, dtype: int, causal,
+        scale: float, stream: int, device: int, status_ptr: int = 0, *, simt: bool = False,
+        dropout=None) -> int:
+    """Raw forward call; returns the library's status code.  `causal` is a bool or one of
+    CAUSAL_*; `dropout` is None or ``(p, seed, offset)``."""
+    head = (ctypes.byref(q), ctypes.byref(k), ctypes.byref(v), ctypes.byref(out), ctypes.c_void_p(lse_ptr),
+            dtype, causal_code(causal), ctypes.c_float(scale))
+    tail = (ctypes.c_void_p(stream), device, ctypes.c_void_p(status_ptr))
+    if dropout is not None:
+        p, seed, offset = dropout
+        return load().b200fa_fwd_dropout(*head, ctypes.c_float(p), ctypes.c_uint64(seed), ctypes.c_uint64(offset),
+                                         1 if simt else 0, *tail)
     fn = load().b200fa_fwd_simt if simt else load().b200fa_fwd
-    return fn(ctypes.byref(q), ctypes.byref(k), ctypes.byref(v), ctypes.byref(out), ctypes.c_void_p(lse_ptr),
-              dtype, 1 if causal else 0, ctypes.c_float(scale), ctypes.c_void_p(stream), device,
-              ctypes.c_void_p(status_ptr))
+    return fn(*head, *tail)
 
 
 def bwd(q: Tensor4, k: Tensor4, v: Tensor4, out: Tensor4, dout: Tensor4, lse_ptr: int, dq: Tensor4,
-        dk: Tensor4, dv: Tensor4, workspace_ptr: int, workspace_bytes: int, dtype: int, causal: bool,
+        dk: Tensor4, dv: Tensor4, workspace_ptr: int, workspace_bytes: int, dtype: int, causal,
         scale: float, stream: int, device: int, status_ptr: int = 0, *, simt: bool = False,
-        parts: int = 7) -> int:
+        parts: int = 7, dropout=None) -> int:
     """Raw backward call; returns the library's status code.  `parts` != 7 runs a subset of
-    the three backward kernels (see b200fa_bwd_parts)."""
-    if parts != 7:
-        return load().b200fa_bwd_parts(
-            ctypes.byref(q), ctypes.byref(k), ctypes.byref(v), ctypes.byref(out), ctypes.byref(dout),
+    the three backward kernels (see b200fa_bwd_parts); `dropout` is None or ``(p, seed, offset)``
+    and must repeat the forward's."""
+    head = (ctypes.byref(q), ctypes.byref(k), ctypes.byref(v), ctypes.byref(out), ctypes.byref(dout),
             ctypes.c_void_p(lse_ptr), ctypes.byref(dq), ctypes.byref(dk), ctypes.byref(dv),
-            ctypes.c_void_p(workspace_ptr), ctypes.c_size_t(workspace_bytes), dtype, 1 if causal else 0,
-            ctypes.c_float(scale), ctypes.c_void_p(stream), device, ctypes.c_void_p(status_ptr), parts)
+            ctypes.c_void_p(workspace_ptr), ctypes.c_size_t(workspace_bytes), dtype, causal_code(causal),
+            ctypes.c_float(scale))
+    tail = (ctypes.c_void_p(stream), device, ctypes.c_void_p(status_ptr))
+    if dropout is not None:
+        p, seed, offset = dropout
+        return load().b200fa_bwd_dropout(*head, ctypes.c_float(p), ctypes.c_uint64(seed), ctypes.c_uint64(offset),
+                                         1 if simt else 0, *tail)
+    if parts != 7:
+        return load().b200fa_bwd_parts(*head, *tail, parts)
     fn = load().b200fa_bwd_simt if simt else load().b200fa_bwd
-    return fn(ctypes.byref(q), ctypes.byref(k), ctypes.byref(v), ctypes.byref(out), ctypes.byref(dout),
-              ctypes.c_void_p(lse_ptr), ctypes.byref(dq), ctypes.byref(dk), ctypes.byref(dv),
-              ctypes.c_void_p(workspace_ptr), ctypes.c_size_t(workspace_bytes), dtype, 1 if causal else 0,
-              ctypes.c_float(scale), ctypes.c_void_p(stream), device, ctypes.c_void_p(status_ptr))
+    return fn(*head, *tail)
+
+
+def fwd_splitkv_workspace_bytes(B: int, Hq: int, Hkv: int, Sq: int, Sk: int, D: int) -> int:
+    return int(load().b200fa_fwd_splitkv_workspace_bytes(B, Hq, Hkv, Sq, Sk, D))
+
+
+def fwd_splitkv(q: Tensor4, k: Tensor4, v: Tensor4, out: Tensor4, lse_ptr: int, workspace_ptr: int,
+                workspace_bytes: int, dtype: int, causal, scale: float, stream: int, device: int,
+                status_ptr: int = 0) -> int:
+    """Raw split-KV (decode) forward; returns the library's status code."""
+    return load().b200fa_fwd_splitkv(
+        ctypes.byref(q), ctypes.byref(k), ctypes.byref(v), ctypes.byref(out), ctypes.c_void_p(lse_ptr),
+        ctypes.c_void_p(workspace_ptr), ctypes.c_size_t(workspace_bytes), dtype, causal_code(causal),
+        ctypes.c_float(scale), ctypes.c_void_p(stream), device, ctypes.c_void_p(status_ptr))
+
+
+def dropout_threshold(p: float) -> int:
+    return int(load().b200fa_dropout_threshold(ctypes.c_float(p)))
+
+
+def dropout_bytes_host(seed: int, offset: int, batch_head: int, row: int, col_block: int) -> bytes:
+    """The 16 mask bytes of one Philox call, evaluated on the host by the library's own code."""
+    buf = (ctypes.c_uint8 * 16)()
+    load().b200fa_dropout_bytes_host(seed, offset, batch_head, row, col_block, buf)
+    return bytes(buf)
+
+
+def set_wait_budget(cycles: int) -> None:
+    load().b200fa_set_wait_budget(int(cycles))
+
+
+def wait_budget() -> int:
+    return int(load().b200fa_wait_budget())
+
+
+def status_to_error(status_value: int) -> int:
+    return int(load().b200fa_status_to_error(int(status_value) & 0xFFFFFFFF))
+
+
+def selftest_wait_timeout(status_ptr: int, budget_cycles: int, stream: int, device: int) -> int:
+    return load().b200fa_selftest_wait_timeout(ctypes.c_void_p(status_ptr), int(budget_cycles),
+                                               ctypes.c_void_p(stream), device)
 
 
 def no_alloc_scratch_bytes() -> int:
@@ -174,5 +266,5 @@ def bwd_no_alloc(q: Tensor4, k: Tensor4, v: Tensor4, out: Tensor4, dout: Tensor4
     output; this wrapper allocates nothing either.  Returns the library's status code."""
     return load().b200fa_bwd_no_alloc(
         ctypes.byref(q), ctypes.byref(k), ctypes.byref(v), ctypes.byref(out), ctypes.byref(dout),
-        ctypes.c_void_p(lse_ptr), ctypes.byref(dq), ctypes.byref(dk), ctypes.byref(dv), dtype, 1 if causal else 0,
+        ctypes.c_void_p(lse_ptr), ctypes.byref(dq), ctypes.byref(dk), ctypes.byref(dv), dtype, causal_code(causal),
         ctypes.c_float(scale), ctypes.c_void_p(stream), device, ctypes.c_void_p(status_ptr))

@@ -88,8 +88,14 @@ def mojo_to_copy(self, *, dtype=None, layout=None, device=None, pin_memory=None,
             out._cuda_view().copy_(src._cuda_view(), non_blocking=non_blocking)
         return out
     if target.type == "cpu":
-        cpu = src._to_cpu_tensor(non_blocking=non_blocking)
-        return cpu if out_dtype == cpu.dtype else cpu.to(out_dtype)
+        if out_dtype != src._dtype:
+            # cast on the device first: a host-side cast would read the pinned buffer of an
+            # asynchronous copy before the copy has landed
+            converted = TorchMojoTensor._alloc(src._shape, out_dtype, src._device_index)
+            if converted._numel:
+                converted._cuda_view().copy_(src._cuda_view())
+            src = converted
+        return src._to_cpu_tensor(non_blocking=non_blocking)
     if target.type == "cuda":
         return src._cuda_view().to(device=target, dtype=out_dtype, copy=True)
     raise NotImplementedError(f"mojo tensors cannot be copied to {target}")
@@ -143,6 +149,22 @@ def mojo_add_tensor_(self, other, *, alpha=1):
     o = payload(other)
     t._cuda_view().add_(o._cuda_view() if o is not None else other, alpha=alpha)
     return self
+
+
+@register_aten_op("aten::add.Tensor")
+def mojo_add_tensor(self, other, *, alpha=1):
+    """The autograd engine sums two gradients of the same leaf with this (a tensor used twice in
+    one attention call, e.g. as key and value); an unregistered op inside the engine would take
+    the process down."""
+    a, b = payload(self), payload(other)
+    lhs = a._cuda_view() if a is not None else self
+    rhs = b._cuda_view() if b is not None else other
+    ref = a if a is not None else b
+    result = torch.add(lhs, rhs, alpha=alpha)
+    out = TorchMojoTensor._alloc(tuple(result.shape), result.dtype, ref._device_index)
+    if out._numel:
+        out._cuda_view().copy_(result)
+    return out
 
 
 # ------------------------------------------------------------------------- metadata-only views

@@ -21,7 +21,7 @@ def scaled_dot_product_attention_autograd(query, key, value, attn_mask=None, dro
     if flash_ops.flash_inputs(query, key, value, attn_mask, dropout_p, is_causal, scale, enable_gqa) is None:
         raise NotImplementedError(
             "scaled_dot_product_attention on the mojo device serves only the flash path: fp32/bf16/fp16 "
-            "(B,H,S,D) tensors, head_dim 64 or 128, Sq == Sk when causal, no attn_mask, dropout_p == 0, positive scale, "
+            "(B,H,S,D) tensors, head_dim 64 or 128, no attn_mask, 0 <= dropout_p < 1, positive scale, "
             "and enable_gqa=True when the key/value head count differs (no fallback exists)"
         )
     return torch.ops.aten._scaled_dot_product_flash_attention.default(

@@ -20,7 +20,7 @@ CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB = os.path.join(HERE, "libb200fa.so")
 STAMP = os.path.join(HERE, "libb200fa.hash")
-SOURCES = ("api.cu", "fwd_sm100.cu", "bwd_sm100.cu", "simt.cu")
+SOURCES = ("api.cu", "fwd_sm100.cu", "bwd_sm100.cu", "simt.cu", "decode.cu")
 NVCC_FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-shared", "--threads", "4",

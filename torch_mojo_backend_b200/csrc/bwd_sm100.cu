@@ -21,33 +21,11 @@
 // Both kernels: warps 0-3 and 4-7 are two compute warpgroups that split the 128 score
 // columns of a tile in halves (thread <-> TMEM lane), warps 8 and 9 each issue one of the two
 // independent MMA chains (the dK/dV kernel uses warp 10 for a third), the next warp drives TMA.
-#include "common.cuh"
-#include "ptx.cuh"
+#include <mutex>
 
-#ifdef B200FA_TRACE
-#define TRACE(role, ev)                                                                          \
-  do {                                                                                           \
-    if (p.status != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 &&          \
-        (threadIdx.x & 31) == 0 && trace_n < 2000) {                                             \
-      reinterpret_cast<unsigned long long*>(p.status + 16)[(role) * 2048 + trace_n++] =          \
-          (static_cast<unsigned long long>(clock64()) << 8) | (ev);                              \
-    }                                                                                            \
-  } while (0)
-// per-CTA clock stamps (SM-local clock, plus the SM id) behind the role timelines
-#define CTA_CLOCK(slot)                                                                          \
-  do {                                                                                           \
-    if (p.status != nullptr) {                                                                   \
-      const unsigned long long cta_ =                                                            \
-          blockIdx.x + gridDim.x * (blockIdx.y + static_cast<unsigned long long>(gridDim.y) * blockIdx.z); \
-      unsigned long long* rec_ = reinterpret_cast<unsigned long long*>(p.status + 32848) + cta_ * 8; \
-      rec_[slot] = clock64();                                                                    \
-      if ((slot) == 0) { unsigned sm_; asm volatile("mov.u32 %0, %%smid;" : "=r"(sm_)); rec_[7] = sm_; } \
-    }                                                                                            \
-  } while (0)
-#else
-#define TRACE(role, ev) do {} while (0)
-#define CTA_CLOCK(slot) do {} while (0)
-#endif
+#include "common.cuh"
+#include "philox.cuh"
+#include "ptx.cuh"
 
 namespace b200fa {
 namespace {
@@ -76,7 +54,7 @@ struct BwdCfg {
 };
 
 #define B200FA_WAIT(bar, parity, site) \
-  if (!mbar_wait((bar), (parity), abort_flag, p.status, (site))) goto teardown
+  if (!mbar_wait((bar), (parity), abort_flag, p.status, (site), p.wait_budget)) goto teardown
 
 // ------------------------------------------------------------------------------------------
 // dK / dV kernel.  One CTA = one 128-row K/V tile of one (batch, kv head); it walks every
@@ -85,7 +63,7 @@ struct BwdCfg {
 // dK MMA); then the dV and dK accumulators.  16-bit P^T goes through shared memory instead, so
 // S^T of the next step can be issued while the exponentials of this step are still running.
 // ------------------------------------------------------------------------------------------
-template <int kD, bool kBf16, bool kCausal>
+template <int kD, bool kBf16, bool kCausal, bool kDropout>
 __global__ void __launch_bounds__(kDkdvThreads, 1)
 bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                 const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
@@ -120,10 +98,6 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-#ifdef B200FA_TRACE
-  int trace_n = 0;
-#endif
-  if (threadIdx.x == 0) CTA_CLOCK(0);
   // Block order: (batch, kv head) pairs are walked `sched_group` at a time, few enough that the
   // Q / dO rows they stream stay in L2, and inside such a group the K/V tiles with the most
   // causal work (the earliest) come first, so the last wave of CTAs is made of short ones.
@@ -143,11 +117,15 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   }
   const int group = p.Hq / p.Hkv;
   const int n0 = n_tile * kTile;
-  const int m_start = kCausal ? n_tile : 0;
+  // query row i sees key column j iff j <= i + causal_off: the first query tile with a row that
+  // sees a key of this tile (none: the tile's dK and dV are zero)
+  const int m_start = kCausal ? min(m_tiles, max(0, n0 - p.causal_off) / kTile) : 0;
   const int per_head = m_tiles - m_start;
   const int steps = group * per_head;
 
-  // The swizzled tiles assume a 1024-byte aligned shared-memory window.
+  // A launch whose status word already reports a failed wait is not worth running; the swizzled
+  // tiles assume a 1024-byte aligned shared-memory window.
+  if (status_is_set(p.status)) return;
   if ((smem_u32(smem) & 1023u) != 0u) {
     if (threadIdx.x == 0 && p.status) atomicCAS(p.status, kStatusOk, 0x414c0000u);
     return;
@@ -188,7 +166,6 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (threadIdx.x == 0) CTA_CLOCK(1);
 
   if (warp < 16) {
     // =========================== compute warps ===========================
@@ -215,7 +192,6 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
       // lse2 rode in with the Q tile; observing its barrier directly makes the bulk copy visible here
       B200FA_WAIT(&q_full[stage], ring_phase, 0x501);
       tc_fence_after();
-      if ((warp & 3) == 0) TRACE(wg & 1, 1);
       float pf[32];
       {
         tmem_ld32(tS, reinterpret_cast<uint32_t*>(pf));
@@ -231,32 +207,53 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         pf[e4 * 4 + 2] = ex2_approx(fmaf(pf[e4 * 4 + 2], c, -l4.z));
         pf[e4 * 4 + 3] = ex2_approx(fmaf(pf[e4 * 4 + 3], c, -l4.w));
       }
-      if (kCausal && m_tile == n_tile) {
-        // on the diagonal tile, query column q sees key row j only if j <= q
+      if (kCausal && n0 + kTile - 1 > m_tile * kTile + p.causal_off) {
+        // a tile the diagonal crosses: query column q sees key row j only if j <= q + causal_off
+        const int first_q = n0 + j - p.causal_off - (m_tile * kTile + wg * 32);  // first column (of these 32) that sees key j
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
-          if (j > wg * 32 + e) pf[e] = 0.f;
+          if (e < first_q) pf[e] = 0.f;
+        }
+      }
+      // dropout: bit e of `keep` <-> query column e of these 32.  Lane L draws the bits of query
+      // row L against this warp's 32 key rows (two Philox calls), and 32 ballots transpose them.
+      uint32_t keep = 0xffffffffu;
+      if constexpr (kDropout) {
+        const int h_now = hk * group + i / per_head;
+        const int q_glob = m_tile * kTile + wg * 32 + lane;
+        const int blk = (n0 + (warp & 3) * 32) >> 4;
+        const uint32_t mine = dropout_bits16(p.drop, b * p.Hq + h_now, q_glob, blk) |
+                              (dropout_bits16(p.drop, b * p.Hq + h_now, q_glob, blk + 1) << 16);
+        keep = 0;
+#pragma unroll
+        for (int jj = 0; jj < 32; ++jj) {
+          const uint32_t word = __ballot_sync(0xffffffffu, (mine >> jj) & 1u);
+          if (lane == jj) keep = word;
         }
       }
       // the previous step's dV MMA must have finished reading the P^T tile
       if (i > 0) { B200FA_WAIT(p_empty, (i - 1) & 1, 0x502); }
 #pragma unroll
       for (int chunk = 0; chunk < 4; ++chunk) {
+        float pd[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          pd[e] = pf[chunk * 8 + e];
+          if constexpr (kDropout) pd[e] = ((keep >> (chunk * 8 + e)) & 1u) ? pd[e] * p.drop.inv_keep : 0.f;
+        }
         uint4 w;
-        w.x = pack2<kBf16>(pf[chunk * 8 + 0], pf[chunk * 8 + 1]);
-        w.y = pack2<kBf16>(pf[chunk * 8 + 2], pf[chunk * 8 + 3]);
-        w.z = pack2<kBf16>(pf[chunk * 8 + 4], pf[chunk * 8 + 5]);
-        w.w = pack2<kBf16>(pf[chunk * 8 + 6], pf[chunk * 8 + 7]);
+        w.x = pack2<kBf16>(pd[0], pd[1]);
+        w.y = pack2<kBf16>(pd[2], pd[3]);
+        w.z = pack2<kBf16>(pd[4], pd[5]);
+        w.w = pack2<kBf16>(pd[6], pd[7]);
         *reinterpret_cast<uint4*>(p_row + (((chunk0 + chunk) ^ (j & 7)) << 4)) = w;
       }
       fence_proxy_async_smem();
       mbar_arrive_warp(p_full);
-      if ((warp & 3) == 0) TRACE(wg & 1, 2);
       // ---- dS^T = P^T * (dP^T - dpsum)
       B200FA_WAIT(dp_full, i & 1, 0x510);
       B200FA_WAIT(&do_full[stage], ring_phase, 0x511);
       tc_fence_after();
-      if ((warp & 3) == 0) TRACE(wg & 1, 3);
       {
         uint32_t d[32];
         tmem_ld32(tDP, d);
@@ -266,10 +263,19 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
 #pragma unroll
         for (int e4 = 0; e4 < 8; ++e4) {
           const float4 d4 = dps[e4];
-          const float a0 = pf[e4 * 4 + 0] * (df[e4 * 4 + 0] - d4.x);
-          const float a1 = pf[e4 * 4 + 1] * (df[e4 * 4 + 1] - d4.y);
-          const float a2 = pf[e4 * 4 + 2] * (df[e4 * 4 + 2] - d4.z);
-          const float a3 = pf[e4 * 4 + 3] * (df[e4 * 4 + 3] - d4.w);
+          float g0 = df[e4 * 4 + 0], g1 = df[e4 * 4 + 1], g2 = df[e4 * 4 + 2], g3 = df[e4 * 4 + 3];
+          if constexpr (kDropout) {
+            // the gradient reaches a probability only through the entries that were kept
+            const uint32_t kb = keep >> (e4 * 4);
+            g0 = (kb & 1u) ? g0 * p.drop.inv_keep : 0.f;
+            g1 = (kb & 2u) ? g1 * p.drop.inv_keep : 0.f;
+            g2 = (kb & 4u) ? g2 * p.drop.inv_keep : 0.f;
+            g3 = (kb & 8u) ? g3 * p.drop.inv_keep : 0.f;
+          }
+          const float a0 = pf[e4 * 4 + 0] * (g0 - d4.x);
+          const float a1 = pf[e4 * 4 + 1] * (g1 - d4.y);
+          const float a2 = pf[e4 * 4 + 2] * (g2 - d4.z);
+          const float a3 = pf[e4 * 4 + 3] * (g3 - d4.w);
           pk[e4 * 2] = pack2<kBf16>(a0, a1);
           pk[e4 * 2 + 1] = pack2<kBf16>(a2, a3);
         }
@@ -278,12 +284,10 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive_warp(ds_full);
-      if ((warp & 3) == 0) TRACE(wg & 1, 4);
     }
     // ---- epilogue: dV and dK (this warpgroup's quarter of the head dimension)
     B200FA_WAIT(acc_full, 0, 0x520);
     tc_fence_after();
-    if (threadIdx.x == 0) CTA_CLOCK(2);
     {
       // The 16-bit dV and dK tiles are staged in the Q / dO ring (every MMA that read it has
       // completed) in the swizzled box layout and leave through TMA stores: whole 128-byte
@@ -295,8 +299,14 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         const uint32_t tacc = tmem_base + lane_off + (which == 0 ? kTmemDV : kTmemDK) + wg * kQuarter;
         const float mul = which == 0 ? 1.f : p.scale;
         uint32_t a[kQuarter];
-        if constexpr (kQuarter == 32) tmem_ld32(tacc, a); else tmem_ld16(tacc, a);
-        tmem_wait_ld();
+        if (steps > 0) {
+          if constexpr (kQuarter == 32) tmem_ld32(tacc, a); else tmem_ld16(tacc, a);
+          tmem_wait_ld();
+        } else {
+          // no query row sees this K/V tile: nothing was accumulated, the gradients are zero
+#pragma unroll
+          for (int e = 0; e < kQuarter; ++e) a[e] = 0u;
+        }
         const float* af = reinterpret_cast<const float*>(a);
 #pragma unroll
         for (int v = 0; v < kQuarter / 8; ++v) {
@@ -359,22 +369,21 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         for (int i = 0; i < steps; ++i) {
           const int stage = i % Cfg::kStages;
           B200FA_WAIT(&q_full[stage], static_cast<uint32_t>((i / Cfg::kStages) & 1), 0x711);
-          TRACE(3, 26);
           // the dK MMA of step i - 2 must have consumed dS^T from this work buffer
           if (i >= 2) { B200FA_WAIT(&buf_free[i & 1], ((i >> 1) - 1) & 1, 0x714); }
           tc_fence_after();
-          TRACE(3, 24);
           issue_kmajor(tWork + (i & 1) * 128, kK, kQ, stage * kStageLo);
           umma_commit(&s_full[i & 1]);
-          TRACE(3, 25);
         }
       } else if (warp == 17) {
         B200FA_WAIT(kv_full, 0, 0x720);
-        B200FA_WAIT(&do_full[0], 0, 0x702);
-        B200FA_WAIT(s_free, 0, 0x703);     // dP^T goes where S^T was once it sits in registers
-        tc_fence_after();
-        issue_kmajor(tWork, kV, kDO, 0);
-        umma_commit(dp_full);
+        if (steps > 0) {
+          B200FA_WAIT(&do_full[0], 0, 0x702);
+          B200FA_WAIT(s_free, 0, 0x703);     // dP^T goes where S^T was once it sits in registers
+          tc_fence_after();
+          issue_kmajor(tWork, kV, kDO, 0);
+          umma_commit(dp_full);
+        }
         for (int i = 0; i < steps; ++i) {
           const int stage = i % Cfg::kStages;
           const uint32_t stage_lo = stage * kStageLo;
@@ -383,7 +392,6 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
           B200FA_WAIT(&q_full[stage], static_cast<uint32_t>((i / Cfg::kStages) & 1), 0x716);
           B200FA_WAIT(ds_full, i & 1, 0x712);
           tc_fence_after();
-          TRACE(4, 23);
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
             const uint32_t a_col = (kk >> 1) * 32 + (kk & 1) * 8;
@@ -393,7 +401,6 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
           }
           umma_commit(&qdo_empty[stage]);   // this lane is done with Q_i (dK) and dO_i (dP^T)
           umma_commit(&buf_free[i & 1]);
-          TRACE(4, 28);
           if (i + 1 < steps) {
             // dP^T of the next step replaces S^T of the next step in the other work buffer
             const int nstage = (i + 1) % Cfg::kStages;
@@ -413,7 +420,6 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
           B200FA_WAIT(&do_full[stage], static_cast<uint32_t>((i / Cfg::kStages) & 1), 0x715);
           B200FA_WAIT(p_full, i & 1, 0x710);
           tc_fence_after();
-          TRACE(5, 21);
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
             const uint32_t a_off = umma_off((kk >> 2) * kSubTileBytes + (kk & 3) * 32);
@@ -423,7 +429,6 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
           }
           umma_commit(p_empty);
           umma_commit(&qdo_empty[stage]);   // this lane is done with dO_i; S^T of Q_i completed long ago
-          TRACE(5, 27);
         }
         umma_commit(acc_full);
       }
@@ -446,7 +451,6 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         if (i >= Cfg::kStages) {
           B200FA_WAIT(&qdo_empty[stage], ((i / Cfg::kStages) - 1) & 1, 0x800);
         }
-        TRACE(6, 30);
         const int64_t stat_off = (static_cast<int64_t>(b) * p.Hq + h) * p.Spad + m_tile * kTile;
         float* st = sStat + stage * 256;
         uint8_t* q_dst = sQ + stage * 2 * Cfg::kTileBytes;
@@ -461,14 +465,12 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   }
 
 teardown:
-  if (threadIdx.x == 0) CTA_CLOCK(3);
   tc_fence_before();
   __syncthreads();
   if (warp == 16) {
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
-    if (lane == 0) CTA_CLOCK(4);
   }
 }
 
@@ -478,7 +480,7 @@ teardown:
 // scalars.  TMEM columns: S double-buffered at [0,128) and [128,256) (16-bit dS overwrites
 // the buffer it was computed from), dP at [256,384), the dQ accumulator after that.
 // ------------------------------------------------------------------------------------------
-template <int kD, bool kBf16, bool kCausal>
+template <int kD, bool kBf16, bool kCausal, bool kDropout>
 __global__ void __launch_bounds__(kThreads, 1)
 bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
               const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
@@ -509,18 +511,22 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-#ifdef B200FA_TRACE
-  int trace_n = 0;
-#endif
-  if (threadIdx.x == 0) CTA_CLOCK(0);
   const int m_tiles = (p.S + kTile - 1) / kTile;
   const int m_tile = m_tiles - 1 - static_cast<int>(blockIdx.x);  // heaviest (latest) causal tiles first
   const int h = blockIdx.y;
   const int b = blockIdx.z;
   const int hk = h / (p.Hq / p.Hkv);
   const int m0 = m_tile * kTile;
-  const int n_tiles = kCausal ? (m_tile + 1) : (p.Sk + kTile - 1) / kTile;
+  // query row i sees key column j iff j <= i + causal_off: K/V tiles up to the one the tile's
+  // last real row still sees (none: dQ of the tile is zero)
+  const int nkv_total = (p.Sk + kTile - 1) / kTile;
+  int n_tiles = nkv_total;
+  if (kCausal) {
+    const int last = min(m0 + kTile - 1, p.S - 1) + p.causal_off;
+    n_tiles = last < 0 ? 0 : min(nkv_total, last / kTile + 1);
+  }
 
+  if (status_is_set(p.status)) return;
   if ((smem_u32(smem) & 1023u) != 0u) {
     if (threadIdx.x == 0 && p.status) atomicCAS(p.status, kStatusOk, 0x414c0001u);
     return;
@@ -559,7 +565,6 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (threadIdx.x == 0) CTA_CLOCK(1);
 
   if (warp < 8) {
     // =========================== compute warps ===========================
@@ -576,7 +581,6 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
       const uint32_t tS = tmem_base + lane_off + kTmemS + buf * 128 + wg * 64;
       B200FA_WAIT(&s_full[buf], (j >> 1) & 1, 0x900);
       tc_fence_after();
-      if ((warp & 3) == 0) TRACE(wg, 1);
       float pf[64];
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
@@ -586,17 +590,27 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
         const float* sf = reinterpret_cast<const float*>(s);
 #pragma unroll
         for (int e = 0; e < 32; ++e) pf[ch * 32 + e] = ex2_approx(fmaf(sf[e], c, -lse2));
-        if (kCausal && j == m_tile) {
-          // diagonal tile: query row r sees key column only if column <= r
+        if (kCausal && j * kTile + kTile - 1 > m0 + p.causal_off) {
+          // a tile the diagonal crosses: query row r sees a key column only if column <= r + causal_off
+          const int last_e = m0 + r + p.causal_off - (j * kTile + wg * 64 + ch * 32);   // last visible of these 32
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
-            if (wg * 64 + ch * 32 + e > r) pf[ch * 32 + e] = 0.f;
+            if (e > last_e) pf[ch * 32 + e] = 0.f;
           }
+        }
+      }
+      uint32_t keep[2] = {0xffffffffu, 0xffffffffu};   // dropout: bit e of keep[ch] <-> key column ch*32 + e of this half
+      if constexpr (kDropout) {
+        const int blk = (j * kTile + wg * 64) >> 4;
+        const int bh = b * p.Hq + h;
+#pragma unroll
+        for (int ch = 0; ch < 2; ++ch) {
+          keep[ch] = dropout_bits16(p.drop, bh, m0 + r, blk + 2 * ch) |
+                     (dropout_bits16(p.drop, bh, m0 + r, blk + 2 * ch + 1) << 16);
         }
       }
       B200FA_WAIT(dp_full, j & 1, 0x910);
       tc_fence_after();
-      if ((warp & 3) == 0) TRACE(wg, 3);
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
         uint32_t d[32];
@@ -606,8 +620,14 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-          const float a0 = pf[ch * 32 + 2 * e] * (df[2 * e] - dps);
-          const float a1 = pf[ch * 32 + 2 * e + 1] * (df[2 * e + 1] - dps);
+          float g0 = df[2 * e], g1 = df[2 * e + 1];
+          if constexpr (kDropout) {
+            const uint32_t kb = keep[ch] >> (2 * e);
+            g0 = (kb & 1u) ? g0 * p.drop.inv_keep : 0.f;
+            g1 = (kb & 2u) ? g1 * p.drop.inv_keep : 0.f;
+          }
+          const float a0 = pf[ch * 32 + 2 * e] * (g0 - dps);
+          const float a1 = pf[ch * 32 + 2 * e + 1] * (g1 - dps);
           pk[e] = pack2<kBf16>(a0, a1);
         }
         tmem_st16(tS + ch * 16, pk);
@@ -615,12 +635,10 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive_warp(ds_full);
-      if ((warp & 3) == 0) TRACE(wg, 4);
     }
     // ---- epilogue: dQ (this warpgroup's half of the head dimension)
     B200FA_WAIT(acc_full, 0, 0x920);
     tc_fence_after();
-    if (threadIdx.x == 0) CTA_CLOCK(2);
     {
       // The scaled 16-bit dQ tile is staged in the Q buffer (every MMA that read it has
       // completed) in the swizzled box layout and leaves through TMA stores: whole 128-byte
@@ -631,8 +649,14 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
 #pragma unroll
       for (int ch = 0; ch < kHalf / 32; ++ch) {
         uint32_t a[32];
-        tmem_ld32(tacc + ch * 32, a);
-        tmem_wait_ld();
+        if (n_tiles > 0) {
+          tmem_ld32(tacc + ch * 32, a);
+          tmem_wait_ld();
+        } else {
+          // no key is visible from this query tile: nothing was accumulated, dQ is zero
+#pragma unroll
+          for (int e = 0; e < 32; ++e) a[e] = 0u;
+        }
         const float* af = reinterpret_cast<const float*>(a);
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
@@ -678,11 +702,13 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
       constexpr uint32_t kTileLo = umma_off(Cfg::kTileBytes);
       if (warp == 8) {
         // prologue: S_0, S_1
-        B200FA_WAIT(qdo_full, 0, 0xa00);
-        B200FA_WAIT(&k_full[0], 0, 0xa01);
-        tc_fence_after();
-        issue_kmajor(tmem_base + kTmemS, kQ, kK, 0);
-        umma_commit(&s_full[0]);
+        if (n_tiles > 0) {
+          B200FA_WAIT(qdo_full, 0, 0xa00);
+          B200FA_WAIT(&k_full[0], 0, 0xa01);
+          tc_fence_after();
+          issue_kmajor(tmem_base + kTmemS, kQ, kK, 0);
+          umma_commit(&s_full[0]);
+        }
         if (n_tiles > 1) {
           B200FA_WAIT(&k_full[1], 0, 0xa02);
           tc_fence_after();
@@ -697,7 +723,6 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
           // compute has written dS_j over S_j
           B200FA_WAIT(ds_full, j & 1, 0xa10);
           tc_fence_after();
-          TRACE(3, 21);
           // dQ += dS_j K_j   (A = 16-bit dS in the S_j columns, B = K_j rows as the contraction index)
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
@@ -711,14 +736,13 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
             // S of tile j+2 re-uses this S buffer
             B200FA_WAIT(&k_full[k2slot], static_cast<uint32_t>(((j + 2) / 3) & 1), 0xa11);
             tc_fence_after();
-            TRACE(3, 22);
             issue_kmajor(tSj, kQ, kK, k2slot * kTileLo);
             umma_commit(&s_full[buf]);
           }
           if (++kslot == 3) kslot = 0;
         }
         umma_commit(acc_full);
-      } else {
+      } else if (n_tiles > 0) {
         // dP_0, then dP_{j+1} whenever the compute warps have consumed dP_j
         B200FA_WAIT(qdo_full, 0, 0xa20);
         B200FA_WAIT(&v_full[0], 0, 0xa03);
@@ -744,18 +768,18 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
 #pragma unroll
         for (int cs = 0; cs < Cfg::kSub; ++cs) tma_load_4d(dst + cs * kSubTileBytes, map, bar, cs * 64, srow, head, b);
       };
-      mbar_arrive_expect_tx(qdo_full, 2 * Cfg::kTileBytes);
-      load_tile(&mapQ, sQ, qdo_full, m0, h);
-      load_tile(&mapDO, sDO, qdo_full, m0, h);
+      if (n_tiles > 0) {
+        mbar_arrive_expect_tx(qdo_full, 2 * Cfg::kTileBytes);
+        load_tile(&mapQ, sQ, qdo_full, m0, h);
+        load_tile(&mapDO, sDO, qdo_full, m0, h);
+      }
       int kslot = 0;
       for (int j = 0; j < n_tiles; ++j) {
         if (j >= 3) { B200FA_WAIT(&k_empty[kslot], static_cast<uint32_t>((j / 3 - 1) & 1), 0xb00); }
-        TRACE(4, 30);
         mbar_arrive_expect_tx(&k_full[kslot], Cfg::kTileBytes);
         load_tile(&mapK, sK + kslot * Cfg::kTileBytes, &k_full[kslot], j * kTile, hk);
         const int vslot = j & 1;
         if (j >= 2) { B200FA_WAIT(&v_empty[vslot], ((j >> 1) - 1) & 1, 0xb01); }
-        TRACE(4, 31);
         mbar_arrive_expect_tx(&v_full[vslot], Cfg::kTileBytes);
         load_tile(&mapV, sV + vslot * Cfg::kTileBytes, &v_full[vslot], j * kTile, hk);
         if (++kslot == 3) kslot = 0;
@@ -764,14 +788,12 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
   }
 
 teardown:
-  if (threadIdx.x == 0) CTA_CLOCK(3);
   tc_fence_before();
   __syncthreads();
   if (warp == 8) {
     __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
-    if (lane == 0) CTA_CLOCK(4);
   }
 }
 #undef B200FA_WAIT
@@ -828,25 +850,36 @@ __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const BwdParams p) 
   for (int off = kLanesPerRow / 2; off >= 1; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
   if (li == 0) {
     p.dpsum[row_global] = (s < p.S) ? acc : 0.f;
-    p.lse_log2[row_global] =
-        (s < p.S) ? p.lse[(static_cast<int64_t>(b) * p.Hq + h) * p.S + s] * 1.4426950408889634f : INFINITY;
+    // a row that saw no key (lse = -inf) gets +inf like the padding rows: its probabilities vanish
+    float l2 = INFINITY;
+    if (s < p.S) {
+      const float l = p.lse[(static_cast<int64_t>(b) * p.Hq + h) * p.S + s];
+      if (l != -INFINITY) l2 = l * 1.4426950408889634f;
+    }
+    p.lse_log2[row_global] = l2;
   }
 }
 
 // The dK/dV kernel and the dQ kernel only depend on the preprocess kernel, not on each other.
 // Run back to back on one stream, the second cannot start until the last, partly idle wave of
 // the first has drained; forked onto a side stream its CTAs fill those SMs as they free up.
-// One side stream and one fork/join event pair per host thread and device, created on first
-// use and kept for the life of the thread.
+// Every device owns a small pool of side streams, each with a fork/join event pair, created on
+// first use and kept until the process exits; the caller's stream handle picks the pool entry,
+// so backward passes issued on different streams do not queue behind one another.  The mutex
+// covers one call's record / wait / launch / record / wait sequence on an entry.
 struct SideStream {
   cudaStream_t stream = nullptr;
   cudaEvent_t fork = nullptr, join = nullptr;
   bool tried = false;
+  std::mutex mutex;
 };
-SideStream* side_stream_for(int dev) {
-  thread_local SideStream side[16];
-  if (dev < 0 || dev >= 16) return nullptr;
-  SideStream& s = side[dev];
+constexpr int kSidePool = 4;
+SideStream* side_stream_for(int dev, cudaStream_t caller) {
+  static SideStream pool[64][kSidePool];
+  if (dev < 0 || dev >= 64) return nullptr;
+  const uintptr_t h = reinterpret_cast<uintptr_t>(caller);
+  SideStream& s = pool[dev][(h >> 4 ^ h >> 12) % kSidePool];
+  std::lock_guard<std::mutex> lock(s.mutex);
   if (!s.tried) {
     s.tried = true;
     if (cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) != cudaSuccess ||
@@ -859,12 +892,31 @@ SideStream* side_stream_for(int dev) {
   return s.stream ? &s : nullptr;
 }
 
-template <int kD, bool kBf16, bool kCausal>
+// cudaFuncSetAttribute for one kernel, once per device, safe against concurrent first calls.
+template <typename Kernel>
+cudaError_t allow_dynamic_smem(Kernel kern, int bytes) {
+  static std::once_flag once[64];
+  static cudaError_t result[64];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  std::call_once(once[dev], [&] {
+    result[dev] = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  });
+  return result[dev];
+}
+
+template <int kD, bool kBf16, bool kCausal, bool kDropout>
 cudaError_t launch_one(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mdo,
                        const CUtensorMap& mdq, const CUtensorMap& mdk, const CUtensorMap& mdv, const BwdParams& p,
                        cudaStream_t stream) {
   using Cfg = BwdCfg<kD>;
   cudaError_t e = cudaSuccess;
+  auto k1 = bwd_dkdv_kernel<kD, kBf16, kCausal, kDropout>;
+  auto k2 = bwd_dq_kernel<kD, kBf16, kCausal, kDropout>;
+  if ((e = allow_dynamic_smem(k1, Cfg::kSmemBytes)) != cudaSuccess) return e;
+  if ((e = allow_dynamic_smem(k2, Cfg::kSmemBytes)) != cudaSuccess) return e;
   if (p.parts & 1) {
     constexpr int kRowsPerWarp = 32 / (kD / 8);
     const int64_t total_rows = static_cast<int64_t>(p.B) * p.Hq * p.Spad;
@@ -873,28 +925,20 @@ cudaError_t launch_one(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }
-  auto k1 = bwd_dkdv_kernel<kD, kBf16, kCausal>;
-  auto k2 = bwd_dq_kernel<kD, kBf16, kCausal>;
-  static bool attr_set[16] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 16 && !attr_set[dev]) {
-    e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-    if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-    if (e != cudaSuccess) return e;
-    attr_set[dev] = true;
-  }
   const int tiles = (p.S + kTile - 1) / kTile;        // query tiles: the dQ kernel's grid
   const int kv_tiles = (p.Sk + kTile - 1) / kTile;    // K/V tiles: the dK/dV kernel's grid
   // fork: the dQ kernel goes to the side stream, behind everything enqueued so far.  Only
   // causal problems: their CTAs differ in length, which is what leaves a long partly idle tail;
   // with equal CTAs the tail is short and interleaving the two kernels only costs L2 hits.
-  SideStream* side = (kCausal && (p.parts & 6) == 6 && !(p.parts & 8)) ? side_stream_for(dev) : nullptr;
+  SideStream* side = (kCausal && (p.parts & 6) == 6 && !(p.parts & 8)) ? side_stream_for(dev, stream) : nullptr;
+  std::unique_lock<std::mutex> side_lock;
   if (side) {
+    side_lock = std::unique_lock<std::mutex>(side->mutex);
     e = cudaEventRecord(side->fork, stream);
     if (e == cudaSuccess) e = cudaStreamWaitEvent(side->stream, side->fork, 0);
-    if (e != cudaSuccess) return e;
+    if (e != cudaSuccess) return e;   // nothing has been enqueued on the side stream yet
   }
   if (p.parts & 2) {
     // (batch, kv head) pairs whose streamed Q / dO rows (both, all query heads of the pair)
@@ -907,19 +951,32 @@ cudaError_t launch_one(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
     k1<<<static_cast<unsigned>(kv_tiles * pairs), kDkdvThreads, Cfg::kSmemBytes, stream>>>(
         mq, mk, mv, mdo, mdk, mdv, p, static_cast<int>(sched_group));
     e = cudaGetLastError();
-    if (e != cudaSuccess) return e;
   }
-  if (p.parts & 4) {
+  if (e == cudaSuccess && (p.parts & 4)) {
     k2<<<dim3(tiles, p.Hq, p.B), kThreads, Cfg::kSmemBytes, side ? side->stream : stream>>>(mq, mk, mv, mdo, mdq, p);
     e = cudaGetLastError();
   }
   if (side) {
-    // join: the caller's stream continues only after both kernels
+    // join, whatever happened in between: once the side stream has been made to wait on the
+    // caller's stream it must flow back into it (a stream capture would otherwise stay forked)
     cudaError_t e2 = cudaEventRecord(side->join, side->stream);
     if (e2 == cudaSuccess) e2 = cudaStreamWaitEvent(stream, side->join, 0);
     if (e == cudaSuccess) e = e2;
   }
   return e;
+}
+
+template <int kD, bool kBf16>
+cudaError_t launch_mask(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mdo,
+                        const CUtensorMap& mdq, const CUtensorMap& mdk, const CUtensorMap& mdv, const BwdParams& p,
+                        cudaStream_t stream) {
+  const bool drop = p.drop.threshold != 0;
+  if (p.causal) {
+    return drop ? launch_one<kD, kBf16, true, true>(mq, mk, mv, mdo, mdq, mdk, mdv, p, stream)
+                : launch_one<kD, kBf16, true, false>(mq, mk, mv, mdo, mdq, mdk, mdv, p, stream);
+  }
+  return drop ? launch_one<kD, kBf16, false, true>(mq, mk, mv, mdo, mdq, mdk, mdv, p, stream)
+              : launch_one<kD, kBf16, false, false>(mq, mk, mv, mdo, mdq, mdk, mdv, p, stream);
 }
 
 }  // namespace
@@ -935,15 +992,13 @@ cudaError_t launch_bwd_sm100(const BwdParams& p, int dtype, cudaStream_t stream,
   if (!encode_map_16bit(&mdk, p.dk, p.B, p.Hkv, p.Sk, p.D, kTile, bf16)) return cudaErrorInvalidValue;
   if (!encode_map_16bit(&mdv, p.dv, p.B, p.Hkv, p.Sk, p.D, kTile, bf16)) return cudaErrorInvalidValue;
   cudaError_t e;
-#define B200FA_DISPATCH(D_, BF_, C_) e = launch_one<D_, BF_, C_>(mq, mk, mv, mdo, mdq, mdk, mdv, p, stream)
   if (p.D == 128) {
-    if (bf16) { if (p.causal) B200FA_DISPATCH(128, true, true); else B200FA_DISPATCH(128, true, false); }
-    else      { if (p.causal) B200FA_DISPATCH(128, false, true); else B200FA_DISPATCH(128, false, false); }
+    e = bf16 ? launch_mask<128, true>(mq, mk, mv, mdo, mdq, mdk, mdv, p, stream)
+             : launch_mask<128, false>(mq, mk, mv, mdo, mdq, mdk, mdv, p, stream);
   } else {
-    if (bf16) { if (p.causal) B200FA_DISPATCH(64, true, true); else B200FA_DISPATCH(64, true, false); }
-    else      { if (p.causal) B200FA_DISPATCH(64, false, true); else B200FA_DISPATCH(64, false, false); }
+    e = bf16 ? launch_mask<64, true>(mq, mk, mv, mdo, mdq, mdk, mdv, p, stream)
+             : launch_mask<64, false>(mq, mk, mv, mdo, mdq, mdk, mdv, p, stream);
   }
-#undef B200FA_DISPATCH
   if (e == cudaSuccess && launches) *launches += (p.parts & 1) + ((p.parts >> 1) & 1) + ((p.parts >> 2) & 1);
   return e;
 }

@@ -38,9 +38,6 @@ __device__ __forceinline__ uint32_t elect_one() {
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
 }
-__device__ __forceinline__ void mbar_inval(uint64_t* bar) {
-  asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
 __device__ __forceinline__ void fence_mbar_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
@@ -73,29 +70,36 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity
   return ok;
 }
 
-// Cycle budget for any single wait (~2 s at 2 GHz).  Generous: the longest legitimate
-// wait in these kernels is a few hundred microseconds.
+// Default cycle budget for any single wait (~2 s at 2 GHz).  Generous: the longest legitimate
+// wait in these kernels is a few hundred microseconds.  The host may pass another budget.
 constexpr long long kWaitBudgetCycles = 4000000000LL;
 
 // Bounded wait.  Returns true when the phase completed, false when the CTA is aborting
-// (either this wait ran out of budget or another thread raised the flag).  `abort_flag`
-// lives in shared memory; `status` is the global status word (may be null).
+// (either this wait ran out of its `budget` of SM cycles or another thread raised the flag).
+// `abort_flag` lives in shared memory; `status` is the global status word (may be null).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                          uint32_t* status, uint32_t site) {
+                                          uint32_t* status, uint32_t site, long long budget) {
   if (mbar_try_wait(bar, parity)) return true;
   long long t0 = clock64();
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 255u) == 0u) {
+    if ((++spins & 63u) == 0u) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitBudgetCycles) {
+      if (clock64() - t0 > budget) {
         *abort_flag = 1u;
         if (status) atomicCAS(status, kStatusOk, kStatusWaitTimeout | (site & 0xffffu));
         return false;
       }
     }
   }
+}
+
+// True when an earlier CTA of this launch (or an earlier launch sharing the status word) has
+// already reported a failed wait: later CTAs then leave at once instead of each spending its
+// own budget on a protocol that is known to be broken.
+__device__ __forceinline__ bool status_is_set(const uint32_t* status) {
+  return status != nullptr && *reinterpret_cast<const volatile uint32_t*>(status) != kStatusOk;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -136,13 +140,6 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, u
       ::"r"(smem_u32(smem_dst)),
       "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
-}
-
-// fire-and-forget fp32 vector add into global memory (address 16-byte aligned)
-__device__ __forceinline__ void red_add_v4(float* gdst, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(reinterpret_cast<uint64_t>(gdst)), "f"(a),
-               "f"(b), "f"(c), "f"(d)
-               : "memory");
 }
 
 // ---------------------------------------------------------------------------------------
@@ -205,29 +202,6 @@ __host__ __device__ constexpr uint32_t umma_idesc(bool bf16, bool a_mn_major, bo
   return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((a_mn_major ? 1u : 0u) << 15) |
          ((b_mn_major ? 1u : 0u) << 16) | (static_cast<uint32_t>(n >> 3) << 17) |
          (static_cast<uint32_t>(m >> 4) << 24);
-}
-
-// D[tmem] (+)= A[smem] * B[smem]
-__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                        uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// D[tmem] (+)= A[tmem] * B[smem]   (A: 16-bit elements packed two per 32-bit column)
-__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                        uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(d_tmem),
-      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
 }
 
 // The issuing thread is a single lane, so every instruction between two MMAs sits on the
@@ -333,6 +307,13 @@ __device__ __forceinline__ void reg_dealloc() {
 // named barrier among `nthreads` threads (id 1..15; id 0 is __syncthreads)
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// max of three floats in one instruction
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float y;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+  return y;
 }
 
 __device__ __forceinline__ float ex2_approx(float x) {

@@ -16,6 +16,7 @@
 #include <cuda_fp16.h>
 
 #include "common.cuh"
+#include "philox.cuh"
 
 namespace b200fa {
 namespace {
@@ -104,7 +105,9 @@ __global__ void __launch_bounds__(256) fwd_simt_kernel(const FwdParams p) {
 #pragma unroll
     for (int k = 0; k < kD / 16; ++k) o[i][k] = 0.f;
   }
-  const int n_end = p.causal ? min(p.Sk, m0 + kT) : p.Sk;
+  const bool drop = p.drop.threshold != 0;
+  // query row i sees key column j iff j <= i + causal_off
+  const int n_end = p.causal ? max(0, min(p.Sk, m0 + kT + p.causal_off)) : p.Sk;
   for (int n0 = 0; n0 < n_end; n0 += kT) {
     __syncthreads();
     stage_tile<T, kD>(sK, kD + 1, p.k, b, hk, n0, p.Sk);
@@ -133,7 +136,7 @@ __global__ void __launch_bounds__(256) fwd_simt_kernel(const FwdParams p) {
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         const int col = n0 + tx + 16 * k;
-        const bool masked = (col >= p.Sk) || (p.causal && col > qr);
+        const bool masked = (col >= p.Sk) || (p.causal && col > qr + p.causal_off);
         s[i][k] = masked ? -INFINITY : s[i][k];
         mx = fmaxf(mx, s[i][k]);
       }
@@ -145,8 +148,9 @@ __global__ void __launch_bounds__(256) fwd_simt_kernel(const FwdParams p) {
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         const float pv = exp2f((s[i][k] - m_new) * c);
-        rs += pv;
-        sP[(ty + 16 * i) * (kT + 1) + tx + 16 * k] = pv;
+        rs += pv;   // the row sum keeps every probability; only what multiplies V is dropped
+        const bool kept = !drop || dropout_keep(p.drop, b * p.Hq + h, qr, n0 + tx + 16 * k);
+        sP[(ty + 16 * i) * (kT + 1) + tx + 16 * k] = kept ? pv : 0.f;
       }
       rs = half_warp_sum(rs);
       lrow[i] = lrow[i] * corr + rs;
@@ -171,11 +175,13 @@ __global__ void __launch_bounds__(256) fwd_simt_kernel(const FwdParams p) {
   for (int i = 0; i < 4; ++i) {
     const int qr = m0 + ty + 16 * i;
     if (qr < p.Sq) {
-      const float inv = 1.f / lrow[i];
+      // a row that saw no key at all (possible under a bottom-right aligned mask) is 0 with lse -inf
+      const float inv = lrow[i] > 0.f ? (drop ? p.drop.inv_keep : 1.f) / lrow[i] : 0.f;
       T* orow = row_ptr_mut<T>(p.out, b, h, qr);
 #pragma unroll
       for (int k = 0; k < kD / 16; ++k) orow[tx + 16 * k] = from_f32<T>(o[i][k] * inv);
-      if (tx == 0) p.lse[((int64_t)b * p.Hq + h) * p.Sq + qr] = mrow[i] * p.scale + logf(lrow[i]);
+      if (tx == 0)
+        p.lse[((int64_t)b * p.Hq + h) * p.Sq + qr] = lrow[i] > 0.f ? mrow[i] * p.scale + logf(lrow[i]) : -INFINITY;
     }
   }
 }
@@ -200,6 +206,7 @@ __global__ void __launch_bounds__(256) bwd_dkdv_simt_kernel(const BwdParams p) {
   const int hk = blockIdx.y, b = blockIdx.z;
   const int group = p.Hq / p.Hkv;
   const float c = p.scale_log2;
+  const bool drop = p.drop.threshold != 0;
 
   stage_tile<T, kD>(sK, kD + 1, p.k, b, hk, n0, p.Sk);
   stage_tile<T, kD>(sV, kD + 1, p.v, b, hk, n0, p.Sk);
@@ -212,14 +219,19 @@ __global__ void __launch_bounds__(256) bwd_dkdv_simt_kernel(const BwdParams p) {
 
   for (int g = 0; g < group; ++g) {
     const int h = hk * group + g;
-    const int m_begin = p.causal ? (n0 / kT) * kT : 0;
+    const int m_begin = p.causal ? (max(0, n0 - p.causal_off) / kT) * kT : 0;
     for (int m0 = m_begin; m0 < p.S; m0 += kT) {
       __syncthreads();
       stage_tile<T, kD>(sQ, kD + 1, p.q, b, h, m0, p.S);
       stage_tile<T, kD>(sdO, kD + 1, p.dout, b, h, m0, p.S);
       if (threadIdx.x < kT) {
         const int qr = m0 + threadIdx.x;
-        sLse[threadIdx.x] = (qr < p.S) ? p.lse[((int64_t)b * p.Hq + h) * p.S + qr] * kLog2e : INFINITY;
+        float l2 = INFINITY;   // rows past the end, and rows that saw no key (lse = -inf): P = 0
+        if (qr < p.S) {
+          const float l = p.lse[((int64_t)b * p.Hq + h) * p.S + qr];
+          if (l != -INFINITY) l2 = l * kLog2e;
+        }
+        sLse[threadIdx.x] = l2;
         sDps[threadIdx.x] = (qr < p.S) ? p.dpsum[((int64_t)b * p.Hq + h) * p.Spad + qr] : 0.f;
       }
       __syncthreads();
@@ -258,10 +270,12 @@ __global__ void __launch_bounds__(256) bwd_dkdv_simt_kernel(const BwdParams p) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const int kc = n0 + tx + 16 * j;
-          const bool masked = (kc >= p.Sk) || (qr >= p.S) || (p.causal && kc > qr);
+          const bool masked = (kc >= p.Sk) || (qr >= p.S) || (p.causal && kc > qr + p.causal_off);
           const float pv = masked ? 0.f : exp2f(s[i][j] * c - sLse[ql]);
-          ds[i][j] = pv * (dp[i][j] - sDps[ql]);
-          sP[ql * (kT + 1) + tx + 16 * j] = pv;
+          // dropout multiplier of this entry: 0 or 1 / (1 - p)
+          const float dm = !drop ? 1.f : (dropout_keep(p.drop, b * p.Hq + h, qr, kc) ? p.drop.inv_keep : 0.f);
+          ds[i][j] = pv * (dp[i][j] * dm - sDps[ql]);
+          sP[ql * (kT + 1) + tx + 16 * j] = pv * dm;
         }
       }
       __syncthreads();
@@ -336,7 +350,11 @@ __global__ void __launch_bounds__(256) bwd_dq_simt_kernel(const BwdParams p) {
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int qr = m0 + ty + 16 * i;
-    lse2[i] = (qr < p.S) ? p.lse[((int64_t)b * p.Hq + h) * p.S + qr] * kLog2e : INFINITY;
+    lse2[i] = INFINITY;
+    if (qr < p.S) {
+      const float l = p.lse[((int64_t)b * p.Hq + h) * p.S + qr];
+      if (l != -INFINITY) lse2[i] = l * kLog2e;
+    }
     dps[i] = (qr < p.S) ? p.dpsum[((int64_t)b * p.Hq + h) * p.Spad + qr] : 0.f;
   }
   float dq[4][kD / 16];
@@ -345,7 +363,8 @@ __global__ void __launch_bounds__(256) bwd_dq_simt_kernel(const BwdParams p) {
 #pragma unroll
     for (int k = 0; k < kD / 16; ++k) dq[i][k] = 0.f;
 
-  const int n_end = p.causal ? min(p.Sk, m0 + kT) : p.Sk;
+  const bool drop = p.drop.threshold != 0;
+  const int n_end = p.causal ? max(0, min(p.Sk, m0 + kT + p.causal_off)) : p.Sk;
   for (int n0 = 0; n0 < n_end; n0 += kT) {
     __syncthreads();
     stage_tile<T, kD>(sK, kD + 1, p.k, b, hk, n0, p.Sk);
@@ -383,9 +402,10 @@ __global__ void __launch_bounds__(256) bwd_dq_simt_kernel(const BwdParams p) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int kc = n0 + tx + 16 * j;
-        const bool masked = (kc >= p.Sk) || (qr >= p.S) || (p.causal && kc > qr);
+        const bool masked = (kc >= p.Sk) || (qr >= p.S) || (p.causal && kc > qr + p.causal_off);
         const float pv = masked ? 0.f : exp2f(s[i][j] * c - lse2[i]);
-        sP[ql * (kT + 1) + tx + 16 * j] = pv * (dp[i][j] - dps[i]);
+        const float dm = !drop ? 1.f : (dropout_keep(p.drop, b * p.Hq + h, qr, kc) ? p.drop.inv_keep : 0.f);
+        sP[ql * (kT + 1) + tx + 16 * j] = pv * (dp[i][j] * dm - dps[i]);
       }
     }
     __syncthreads();
@@ -416,13 +436,13 @@ __global__ void __launch_bounds__(256) bwd_dq_simt_kernel(const BwdParams p) {
 // dpsum[b,h,s] = sum_d dO * O (fp32), one warp per row.
 template <typename T>
 __global__ void dpsum_simt_kernel(const BwdParams p) {
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int64_t warp = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const int64_t rows = (int64_t)p.B * p.Hq * p.S;
   if (warp >= rows) return;
-  const int s = warp % p.S;
-  const int h = (warp / p.S) % p.Hq;
-  const int b = warp / ((int64_t)p.S * p.Hq);
+  const int s = (int)(warp % p.S);
+  const int h = (int)((warp / p.S) % p.Hq);
+  const int b = (int)(warp / ((int64_t)p.S * p.Hq));
   const T* o = row_ptr<T>(p.out, b, h, s);
   const T* d = row_ptr<T>(p.dout, b, h, s);
   float acc = 0.f;

@@ -1,10 +1,12 @@
-"""The ``torch.mojo`` backend module: device bookkeeping, synchronisation and Philox state.
+"""The ``torch.mojo`` backend module.
 
-Same surface as the reference's device module
-(torch_mojo_backend/mojo_device/torch_mojo_device_module.py:15-199): ``device_count``,
-``current_device``/``set_device``, the ``device`` context manager, ``synchronize`` and the
-per-device ``(seed, counter)`` RNG state with ``_reserve_philox_state``.  Here ``mojo:i`` is
-CUDA device ``i`` of this process (one process per GPU when scaling out).
+torch looks functions up on this module by name (``device_count``, ``current_device``,
+``set_device``, ``device``, ``synchronize``, ``manual_seed_all``, ``get_rng_state`` ...: the
+contract of ``torch.utils.backend_registration``), so the names match the reference's module
+(torch_mojo_backend/mojo_device/torch_mojo_device_module.py:15-199); what is behind them is this
+package's: ``mojo:i`` is CUDA device ``i`` of the process (one process per GPU when scaling out),
+``synchronize`` also surfaces a kernel that gave up on an internal wait, and the per-device
+Philox generator state feeds the dropout mask of the flash-attention kernels.
 """
 
 from __future__ import annotations
@@ -13,12 +15,7 @@ import threading
 
 import torch
 
-_current_device = 0
-_UINT64_MASK = (1 << 64) - 1
-_DEFAULT_RNG_SEED = 67_280_421_310_721
-_rng_default_seed = _DEFAULT_RNG_SEED
-_rng_states: dict[int, tuple[int, int]] = {}
-_rng_lock = threading.Lock()
+_current = 0
 
 
 def _is_in_bad_fork() -> bool:
@@ -38,80 +35,95 @@ def device_count() -> int:
 
 
 def current_device() -> int:
-    return _current_device
+    return _current
 
 
-def set_device(device_idx: int) -> None:
-    global _current_device
-    count = device_count()
-    if device_idx < 0 or (count and device_idx >= count):
-        raise ValueError(f"Invalid device index {device_idx}")
-    _current_device = device_idx
-
-
-class device:
-    """Context manager that swaps the current mojo device (``torch.cuda.device`` analogue;
-    ``torch.serialization`` needs it for ``map_location="mojo"``)."""
-
-    def __init__(self, device: "int | str | torch.device | None") -> None:
-        if device is None:
-            self.idx = -1
-        elif isinstance(device, int):
-            self.idx = device
-        else:
-            index = torch.device(device).index
-            self.idx = -1 if index is None else index
-
-    def __enter__(self) -> None:
-        self.prev_idx = _current_device
-        if self.idx >= 0 and self.idx != _current_device:
-            set_device(self.idx)
-
-    def __exit__(self, *exc_info: object) -> bool:
-        if self.idx >= 0 and self.prev_idx != _current_device:
-            set_device(self.prev_idx)
-        return False
-
-
-def _resolve_index(device: "int | str | torch.device | None") -> int:
-    if device is None:
-        return _current_device
-    if isinstance(device, int):
-        return device
-    torch_device = torch.device(device)
-    if torch_device.type != "mojo":
-        raise ValueError(f"expected a mojo device, got {torch_device}")
-    return _current_device if torch_device.index is None else torch_device.index
-
-
-def synchronize(device: "int | str | torch.device | None" = None) -> None:
-    """Wait for every kernel and copy issued on the device's stream."""
-    torch.cuda.synchronize(_resolve_index(device))
-
-
-# ---------------------------------------------------------------------------- RNG state
-def _normalize_rng_seed(seed) -> int:
-    value = int(seed)
-    if value < -(1 << 63) or value > _UINT64_MASK:
-        raise ValueError("Overflow when unpacking long long")
-    return value & _UINT64_MASK
-
-
-def _rng_device_index(device=None) -> int:
-    index = _resolve_index(device)
+def _checked_index(index: int) -> int:
     count = device_count()
     if index < 0 or (count and index >= count):
         raise ValueError(f"Invalid device index {index}")
     return index
 
 
+def set_device(device_idx: int) -> None:
+    global _current
+    _current = _checked_index(int(device_idx))
+
+
+def _index_of(device) -> int:
+    """Device ordinal of an int / str / torch.device / None (None and index-less: the current one)."""
+    if device is None:
+        return _current
+    if isinstance(device, int):
+        return device
+    dev = torch.device(device)
+    if dev.type != "mojo":
+        raise ValueError(f"expected a mojo device, got {dev}")
+    return _current if dev.index is None else dev.index
+
+
+class device:
+    """``with torch.mojo.device(i):`` — makes ``mojo:i`` current inside the block
+    (``torch.serialization`` relies on it for ``map_location="mojo"``)."""
+
+    def __init__(self, device) -> None:
+        self._target = None if device is None else (device if isinstance(device, int) else torch.device(device).index)
+
+    def __enter__(self) -> None:
+        self._saved = _current
+        if self._target is not None and self._target >= 0:
+            set_device(self._target)
+
+    def __exit__(self, *exc) -> bool:
+        if _current != self._saved:
+            set_device(self._saved)
+        return False
+
+
+def synchronize(device=None) -> None:
+    """Wait for every kernel and copy issued on the device, then raise if one of the
+    flash-attention kernels reported that it gave up on an internal wait."""
+    index = _index_of(device)
+    torch.cuda.synchronize(index)
+    from . import flash_ops
+
+    flash_ops.check_status(index)
+
+
+def get_amp_supported_dtype():
+    return [torch.float16, torch.bfloat16]
+
+
+# ---------------------------------------------------------------------------- Philox generator state
+# Per device: a 64-bit seed and a 64-bit counter.  An op that needs random bits reserves an
+# interval of the counter (``_reserve_philox_state``) and keys its Philox calls with
+# (seed, reserved offset + its own index), so two calls never draw the same numbers and a
+# restored state replays them.  The 16-byte state tensor is seed then counter, little-endian,
+# the same encoding the reference uses (torch_mojo_device_module.py:121-156).
+_U64 = (1 << 64) - 1
+
+
+class _Generators:
+    def __init__(self) -> None:
+        self.lock = threading.Lock()
+        self.default_seed = 67_280_421_310_721   # torch's default CUDA generator seed
+        self.state: dict[int, list[int]] = {}    # index -> [seed, counter]
+
+    def of(self, index: int) -> list[int]:
+        return self.state.setdefault(index, [self.default_seed, 0])
+
+
+_gen = _Generators()
+
+
 def manual_seed_all(seed) -> None:
-    """Reset every device to the same Philox seed and counter zero."""
-    global _rng_default_seed
-    normalized = _normalize_rng_seed(seed)
-    with _rng_lock:
-        _rng_default_seed = normalized
-        _rng_states.clear()
+    """Every device restarts from `seed` with its counter at zero."""
+    value = int(seed)
+    if not -(1 << 63) <= value <= _U64:
+        raise ValueError("Overflow when unpacking long long")
+    with _gen.lock:
+        _gen.default_seed = value & _U64
+        _gen.state.clear()
 
 
 def manual_seed(seed) -> None:
@@ -119,38 +131,34 @@ def manual_seed(seed) -> None:
 
 
 def get_rng_state(device=None) -> torch.Tensor:
-    """The device's exact ``(seed, counter)`` as 16 little-endian bytes."""
-    index = _rng_device_index(device)
-    with _rng_lock:
-        seed, counter = _rng_states.setdefault(index, (_rng_default_seed, 0))
-    encoded = seed.to_bytes(8, "little") + counter.to_bytes(8, "little")
-    return torch.tensor(list(encoded), dtype=torch.uint8)
+    index = _checked_index(_index_of(device))
+    with _gen.lock:
+        seed, counter = _gen.of(index)
+    raw = seed.to_bytes(8, "little") + counter.to_bytes(8, "little")
+    return torch.frombuffer(bytearray(raw), dtype=torch.uint8).clone()
 
 
 def set_rng_state(new_state, device=None) -> None:
     if not isinstance(new_state, torch.Tensor):
         raise TypeError("Mojo RNG state must be a torch.Tensor")
-    state = new_state.detach().cpu().contiguous()
-    if state.dtype != torch.uint8 or state.numel() != 16:
+    flat = new_state.detach().cpu().contiguous().reshape(-1)
+    if flat.dtype != torch.uint8 or flat.numel() != 16:
         raise ValueError("Mojo RNG state must be a 16-element uint8 tensor")
-    encoded = bytes(state.reshape(-1).tolist())
-    index = _rng_device_index(device)
-    with _rng_lock:
-        _rng_states[index] = (int.from_bytes(encoded[:8], "little"), int.from_bytes(encoded[8:], "little"))
+    raw = bytes(flat.tolist())
+    index = _checked_index(_index_of(device))
+    with _gen.lock:
+        _gen.state[index] = [int.from_bytes(raw[:8], "little"), int.from_bytes(raw[8:], "little")]
 
 
 def _reserve_philox_state(device, counter_increment: int) -> tuple[int, int]:
-    """Atomically reserve a Philox counter interval; returns (seed, base counter)."""
+    """Take `counter_increment` values off the device's counter; returns (seed, first value)."""
     if type(counter_increment) is not int or counter_increment < 0:
         raise ValueError("Philox counter increment must be a nonnegative integer")
-    index = _rng_device_index(device)
-    with _rng_lock:
-        seed, counter = _rng_states.setdefault(index, (_rng_default_seed, 0))
-        if counter_increment > _UINT64_MASK - counter:
+    index = _checked_index(_index_of(device))
+    with _gen.lock:
+        entry = _gen.of(index)
+        seed, first = entry
+        if first + counter_increment > _U64:
             raise OverflowError("Philox counter reservation would wrap uint64")
-        _rng_states[index] = (seed, counter + counter_increment)
-    return seed, counter
-
-
-def get_amp_supported_dtype():
-    return [torch.float16, torch.bfloat16]
+        entry[1] = first + counter_increment
+    return seed, first

@@ -143,7 +143,11 @@ class TorchMojoTensor(torch.Tensor):
     def _view_of(cls, base: "TorchMojoTensor", shape, strides, offset, contiguous=None) -> "TorchMojoTensor":
         """A zero-copy view sharing base's holder; `offset` is absolute, in elements."""
         ptr = base._ptr + (int(offset) - base._offset) * base._itemsize
-        return cls._make(base._holder, ptr, shape, strides, offset, base._dtype, base._device_index, contiguous)
+        view = cls._make(base._holder, ptr, shape, strides, offset, base._dtype, base._device_index, contiguous)
+        if hasattr(base, "_philox"):
+            # the (seed, offset) pair an rng_state tensor carries on the host survives detach / alias
+            view._philox = base._philox
+        return view
 
     @classmethod
     def _from_cuda(cls, t: torch.Tensor) -> "TorchMojoTensor":

@@ -1,21 +1,31 @@
-"""Benchmark of the flash-attention hot path: TFLOP/s of one forward+backward step.
+"""Benchmark of the flash-attention hot path: TFLOP/s of one forward(+backward) step.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--config C3] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config C3] [--scaling auto|weak|strong]
+                    [--impl ours|reference]
 
-A "step" is one forward and one backward pass of the attention operator over one batch of
-seeded synthetic tensors.  With N > 1 (launched under ``torch.distributed.run``, one rank per
-GPU) every rank owns an independent batch of the same size — the path shards over
-(batch, kv-head group) units with no collective — so scaling is weak and ``value`` is the
-aggregate over all ranks.  FLOPs follow the reference's convention: forward
-``4*B*Hq*S*S*D`` halved when causal, backward 2.5x forward
-(benchmarks/test_attention.py:46,163).
+A "step" is one forward and (where the configuration has one) one backward pass of the
+attention operator over one batch of seeded synthetic tensors.  The path shards over
+(batch, kv-head group) units with no collective.  With N > 1 (launched under
+``torch.distributed.run``, one rank per GPU):
+
+* ``weak`` scaling (the default for C1-C3): every rank owns an independent batch of the full
+  per-GPU size, drawn from seed = rank; ``value`` is the aggregate over all ranks.
+* ``strong`` scaling (the default for C4 and C5, the two configurations defined as a split of
+  one problem): the full problem is drawn once from seed 0 and rank r takes its contiguous slice
+  of the (batch, kv-head group) units - C4: 32 heads -> 4 per GPU at N = 8; C5: 64 batch entries
+  -> 64/N per GPU.  After the timed region the shards' results are gathered on rank 0 with NCCL
+  ``all_gather`` and compared, bit for bit, with rank 0's own run of the whole problem on one
+  GPU (``validation`` in the JSON line).
+
+FLOPs follow the reference's convention: forward ``4*B*Hq*S*S*D`` halved when causal, backward
+2.5x forward (benchmarks/test_attention.py:46,163).
 
 Rank 0 prints ONE JSON line.  ``value`` is timed with CUDA events on tensors already resident
-in HBM; ``e2e`` runs the same step through the public `mojo`-device operator API with pinned
-HOST buffers, host<->device copies inside the timed region (headline: the batch pipelined in
-pieces over three streams; ``e2e.single_call``: one call over the whole batch on one stream); ``roofline`` times the dominant
-kernel (the backward dK/dV kernel) alone; ``cpu_baseline`` is the CPU oracle timed on the
-host cores on a bounded slice of the same workload.
+in HBM; ``e2e`` runs the same step on HOST tensors through the package's public API
+(``HostAttentionPipeline`` over the `mojo`-device operators; ``e2e.single_call``: one
+``F.scaled_dot_product_attention`` + ``backward`` over the whole batch), host<->device copies
+inside the timed region; ``roofline`` times the dominant kernel alone; ``cpu_baseline`` is the
+CPU oracle timed on the host cores on a bounded slice of the same workload.
 """
 
 from __future__ import annotations
@@ -27,19 +37,22 @@ import statistics
 import subprocess
 import sys
 import threading
-import time
 
 import torch
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-METRIC = "flash-attn fwd+bwd TFLOP/s (bf16, causal)"
 NOMINAL_BF16_TFLOPS = 2250.0
 FALLBACK_BF16_TFLOPS = 1590.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the backward dK/dV kernel on the
-# C3 workload, from the ncu capture summarised in profiles/bwd_dkdv_kernel_C3.md.
-BWD_DKDV_DRAM_TRAFFIC_BYTES = 395.2e6
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from one
+# ncu capture of that kernel on that workload (bytes per launch)
+DRAM_TRAFFIC_BYTES = {("C3", "bwd_dkdv_kernel"): 395.2e6, ("C4", "fwd_kernel"): None}
+
+
+def metric_name(cfg) -> str:
+    dt = str(cfg.dtype).replace("torch.", "").replace("bfloat16", "bf16").replace("float16", "fp16").replace("float32", "fp32")
+    return f"flash-attn {'fwd+bwd' if cfg.backward else 'fwd'} TFLOP/s ({dt}, {'causal' if cfg.causal else 'non-causal'})"
 
 
 def load_peaks():
@@ -138,7 +151,7 @@ class ClockSampler:
         }
 
 
-def dist_setup(n_gpus: int):
+def dist_setup():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -147,6 +160,14 @@ def dist_setup(n_gpus: int):
 
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        # each rank keeps to its own slice of the host cores (its copies and dispatch then do not
+        # migrate across the other ranks' cores)
+        try:
+            cores = sorted(os.sched_getaffinity(0))
+            per = max(1, len(cores) // world)
+            os.sched_setaffinity(0, set(cores[local * per:(local + 1) * per]) or set(cores))
+        except (AttributeError, OSError):
+            pass
     return rank, world, local
 
 
@@ -168,31 +189,111 @@ def max_over_ranks(x: float, world: int) -> float:
     return float(t.item())
 
 
+def shard_slices(cfg, rank: int, world: int):
+    """(batch slice, query-head slice, kv-head slice) of rank `rank`: the contiguous slice of the
+    flattened (batch, kv head) index it owns; the batch is split first, then kv heads with the
+    query heads that read them (a GQA group is never split)."""
+    group = cfg.Hq // cfg.Hkv
+    if cfg.B % world == 0:
+        per = cfg.B // world
+        return slice(rank * per, (rank + 1) * per), slice(None), slice(None)
+    if world % cfg.B == 0 and cfg.Hkv % (world // cfg.B) == 0:
+        ranks_per_entry = world // cfg.B
+        b, part = divmod(rank, ranks_per_entry)
+        hk = cfg.Hkv // ranks_per_entry
+        return slice(b, b + 1), slice(part * hk * group, (part + 1) * hk * group), slice(part * hk, (part + 1) * hk)
+    raise ValueError(f"{cfg.name} does not split over {world} ranks")
+
+
+def attention_step(raw, q, k, v, dout, cfg, bufs, status):
+    raw.flash_fwd(q, k, v, causal=cfg.causal, scale=cfg.scale, out=bufs["out"], lse=bufs["lse"], status=status)
+    if cfg.backward:
+        raw.flash_bwd(dout, q, k, v, bufs["out"], bufs["lse"], causal=cfg.causal, scale=cfg.scale, dq=bufs["dq"],
+                      dk=bufs["dk"], dv=bufs["dv"], workspace=bufs["ws"], status=status)
+
+
+def make_bufs(_lib, raw, q, k, v, cfg):
+    B, Hq, S, D = q.shape
+    code = raw.dtype_code(q.dtype)
+    bufs = {"out": torch.empty_like(q), "lse": torch.empty((B, Hq, S), dtype=torch.float32, device=q.device)}
+    if cfg.backward:
+        bufs.update(dq=torch.empty_like(q), dk=torch.empty_like(k), dv=torch.empty_like(v),
+                    ws=torch.empty((_lib.bwd_workspace_bytes(B, Hq, k.shape[1], S, D, code),), dtype=torch.uint8,
+                                   device=q.device))
+    return bufs
+
+
+def validate_shards(cfg, world, rank, slices, cpu_full, bufs, _lib, raw, dev):
+    """all_gather every rank's out / lse (and dq / dk / dv) to rank 0 and compare, bit for bit,
+    with rank 0's own run of the WHOLE problem on one GPU."""
+    import torch.distributed as dist
+
+    names = ["out", "lse"] + (["dq", "dk", "dv"] if cfg.backward else [])
+    gathered = {}
+    for name in names:
+        mine = bufs[name].contiguous()
+        parts = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(parts, mine)
+        gathered[name] = parts
+    if rank != 0:
+        return None
+    q, k, v, dout = (t.to(dev) for t in cpu_full)
+    full = make_bufs(_lib, raw, q, k, v, cfg)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    attention_step(raw, q, k, v, dout, cfg, full, status)
+    torch.cuda.synchronize()
+    report = {"gathered_with": "nccl all_gather", "ranks": world, "tensors": {}, "status_word": int(status.item())}
+    ok = int(status.item()) == 0
+    for name in names:
+        same = True
+        for r, part in enumerate(gathered[name]):
+            bs, qs, ks = shard_slices(cfg, r, world)
+            hs = ks if name in ("dk", "dv") else qs
+            ref = full[name][bs, hs]
+            same = same and torch.equal(part, ref.contiguous())
+        # a checksum of the reassembled tensor, as evidence that something was compared
+        total = sum(float(p.float().abs().sum().item()) for p in gathered[name])
+        report["tensors"][name] = {"bitwise_equal_to_single_gpu": bool(same), "abs_sum": total}
+        ok = ok and same
+    report["validated"] = bool(ok)
+    return report
+
+
 def run_ours(args):
     from oracle import sdpa_oracle as O  # input generation + (rank 0, N=1) the cpu_baseline leg
     from torch_mojo_backend_b200 import _lib, raw
 
-    rank, world, local = dist_setup(args.gpus)
+    rank, world, local = dist_setup()
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
-    cfg = O.CONFIGS[args.config]
-    do_bwd = cfg.backward
-    q, k, v, dout = (t.to(dev) for t in O.make_inputs(cfg, seed=rank))
-    out = torch.empty_like(q)
-    lse = torch.empty((cfg.B, cfg.Hq, cfg.S), dtype=torch.float32, device=dev)
-    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-    code = raw.dtype_code(cfg.dtype)
-    ws = torch.empty((_lib.bwd_workspace_bytes(cfg.B, cfg.Hq, cfg.Hkv, cfg.S, cfg.D, code),), dtype=torch.uint8,
-                     device=dev)
+    cfg_full = O.CONFIGS[args.config]
+    scaling = args.scaling
+    if scaling == "auto":
+        scaling = "strong" if (world > 1 and args.config in ("C4", "C5")) else "weak"
+    if world == 1:
+        scaling = "weak" if args.scaling == "auto" else scaling
+    do_bwd = cfg_full.backward
+    if scaling == "strong" and world > 1:
+        cpu_full = O.make_inputs(cfg_full, seed=0)
+        slices = shard_slices(cfg_full, rank, world)
+        bs, qs, ks = slices
+        q, k, v, dout = (cpu_full[0][bs, qs].contiguous().to(dev), cpu_full[1][bs, ks].contiguous().to(dev),
+                         cpu_full[2][bs, ks].contiguous().to(dev), cpu_full[3][bs, qs].contiguous().to(dev))
+        cfg = O.shard(cfg_full, rank, world)
+        seed_note = "torch.Generator().manual_seed(0) for the whole problem, sliced per rank"
+    else:
+        cpu_full, slices = None, None
+        cfg = cfg_full
+        q, k, v, dout = (t.to(dev) for t in O.make_inputs(cfg, seed=rank))
+        seed_note = "torch.Generator().manual_seed(rank); q,k,v,dO drawn in that order"
+    bufs = make_bufs(_lib, raw, q, k, v, cfg)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
 
     def step():
-        raw.flash_fwd(q, k, v, causal=cfg.causal, scale=cfg.scale, out=out, lse=lse, status=status)
-        if do_bwd:
-            raw.flash_bwd(dout, q, k, v, out, lse, causal=cfg.causal, scale=cfg.scale, dq=dq, dk=dk, dv=dv,
-                          workspace=ws, status=status)
+        attention_step(raw, q, k, v, dout, cfg, bufs, status)
 
-    for _ in range(max(args.warmup, 3)):
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
         step()
     barrier(world)
     launches0 = _lib.launch_count()
@@ -209,7 +310,7 @@ def run_ours(args):
         # forward-only and single-backward-kernel timings explain the step number
         ef0.record()
         for _ in range(args.steps):
-            raw.flash_fwd(q, k, v, causal=cfg.causal, scale=cfg.scale, out=out, lse=lse, status=status)
+            raw.flash_fwd(q, k, v, causal=cfg.causal, scale=cfg.scale, out=bufs["out"], lse=bufs["lse"], status=status)
         ef1.record()
         torch.cuda.synchronize()
         fwd_ms = ef0.elapsed_time(ef1) / args.steps
@@ -219,8 +320,9 @@ def run_ours(args):
                 eb0, eb1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 eb0.record()
                 for _ in range(args.steps):
-                    raw.flash_bwd(dout, q, k, v, out, lse, causal=cfg.causal, scale=cfg.scale, dq=dq, dk=dk, dv=dv,
-                                  workspace=ws, status=status, parts=part)
+                    raw.flash_bwd(dout, q, k, v, bufs["out"], bufs["lse"], causal=cfg.causal, scale=cfg.scale,
+                                  dq=bufs["dq"], dk=bufs["dk"], dv=bufs["dv"], workspace=bufs["ws"], status=status,
+                                  parts=part)
                 eb1.record()
                 torch.cuda.synchronize()
                 bwd_part_ms[name] = eb0.elapsed_time(eb1) / args.steps
@@ -230,25 +332,32 @@ def run_ours(args):
         raise RuntimeError(f"kernel status word is 0x{int(status.item()) & 0xffffffff:x}")
 
     ms_per_step = total_ms / args.steps
-    step_flops = cfg.fwd_flops() + (cfg.bwd_flops() if do_bwd else 0.0)
-    value = world * step_flops / (ms_per_step * 1e-3) / 1e12
+    flops_of = lambda c: c.fwd_flops() + (c.bwd_flops() if do_bwd else 0.0)
+    # weak: every rank did a full per-GPU problem; strong: together the ranks did the one full problem
+    job_flops = world * flops_of(cfg) if scaling == "weak" else flops_of(cfg_full)
+    value = job_flops / (ms_per_step * 1e-3) / 1e12
 
-    # ---- end to end through the public operator API on the mojo device, host buffers in/out
-    e2e = None if args.no_e2e else run_e2e(cfg, rank, world, local, args)
+    validation = None
+    if scaling == "strong" and world > 1:
+        validation = validate_shards(cfg_full, world, rank, slices, cpu_full, bufs, _lib, raw, dev)
+
+    # ---- end to end on HOST tensors through the package's public API
+    e2e = None if args.no_e2e else run_e2e(cfg, q, k, v, dout, rank, world, local, args)
 
     burst, sustained, peak_src = load_peaks()
     if do_bwd:
         # The dK/dV kernel is the longest launch.  Its algorithmic work is the 4 tile GEMMs of the 5 a
         # backward needs that it covers (S^T, dP^T, dV, dK): 0.8 x the backward FLOPs (2.0 x forward).
-        dom_flops, dom_ms, dom_name = 0.8 * cfg.bwd_flops(), bwd_part_ms["dkdv"], "bwd_dkdv_kernel (S^T, dP^T, dV, dK)"
+        dom_flops, dom_ms, dom_key = 0.8 * cfg.bwd_flops(), bwd_part_ms["dkdv"], "bwd_dkdv_kernel"
+        dom_name = "bwd_dkdv_kernel (S^T, dP^T, dV, dK)"
     else:
-        dom_flops, dom_ms, dom_name = cfg.fwd_flops(), fwd_ms, "fwd_kernel"
+        dom_flops, dom_ms, dom_key, dom_name = cfg.fwd_flops(), fwd_ms, "fwd_kernel", "fwd_kernel"
     achieved = dom_flops / (dom_ms * 1e-3) / 1e12
     roofline = {
         "bound": "tensor", "kernel": dom_name, "achieved": round(achieved, 2), "peak": burst, "unit": "TFLOP/s",
         "frac": round(achieved / burst, 4), "peak_source": f"of {peak_src} (cuBLAS bf16 burst)",
         "frac_of_nominal_2250": round(achieved / NOMINAL_BF16_TFLOPS, 4),
-        "traffic": BWD_DKDV_DRAM_TRAFFIC_BYTES if (do_bwd and cfg.name == "C3") else None,
+        "traffic": DRAM_TRAFFIC_BYTES.get((cfg.name, dom_key)) if world == 1 else None,
         "ms_per_launch": round(dom_ms, 4),
     }
     detail = {
@@ -272,21 +381,24 @@ def run_ours(args):
                         "sample": sample}
 
     if rank == 0:
+        per_gpu = (f"B={cfg.B} Hq={cfg.Hq} Hkv={cfg.Hkv} S={cfg.S} D={cfg.D} per GPU")
+        whole = (f" of the whole B={cfg_full.B} Hq={cfg_full.Hq} Hkv={cfg_full.Hkv}" if scaling == "strong" and world > 1
+                 else "")
         line = {
-            "metric": METRIC, "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": str(cfg.dtype).replace("torch.", ""),
+            "metric": metric_name(cfg_full), "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+            "scaling": scaling, "vs_baseline": None, "dtype": str(cfg.dtype).replace("torch.", ""),
             "data": "synthetic",
             "config": {
                 "workload": f"{cfg.name}: {'causal' if cfg.causal else 'non-causal'} "
-                            f"{'fwd+bwd' if do_bwd else 'fwd'} B={cfg.B} Hq={cfg.Hq} Hkv={cfg.Hkv} S={cfg.S} "
-                            f"D={cfg.D} per GPU",
+                            f"{'fwd+bwd' if do_bwd else 'fwd'} {per_gpu}{whole}",
                 "l2": "inputs larger than L2 (no flush needed)" if cfg.fwd_bytes() > 126e6
                       else "working set fits in L2 (L2-hot number)",
-                "seed": "torch.Generator().manual_seed(rank); q,k,v,dO drawn in that order",
+                "seed": seed_note,
             },
             "frac_of_nominal_2250": round(value / world / NOMINAL_BF16_TFLOPS, 4),
             "detail": detail, "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
+            "validation": validation,
             "gpu_launches": int(launches), "gpu_launches_in_step_region": int(timed_launches),
             "clocks": sampler.summary(),
         }
@@ -297,28 +409,28 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def run_e2e(cfg, rank, world, local, args):
-    """Same step through the `mojo` device's operator API with HOST buffers: pinned host
-    tensors in, out and gradients read back into pinned host tensors, all inside the timed
-    region.  Two ways of driving it are timed:
+def run_e2e(cfg, q_dev, k_dev, v_dev, dout_dev, rank, world, local, args):
+    """The same step on HOST tensors: pinned host q, k, v, dO in, out and the gradients back in
+    pinned host tensors, every copy inside the timed region.  Two ways of driving it are timed:
 
     * ``single_call``: one F.scaled_dot_product_attention call and one ``backward`` over the
-      whole batch, every copy and kernel on one stream (copies and compute in sequence);
-    * the headline: the batch walked one batch entry at a time through
-      ``aten::_scaled_dot_product_flash_attention`` and ``..._backward`` (the two operators the
-      device registers), with uploads, kernels and downloads on three streams, so that PCIe in
-      both directions and the kernels overlap.  Same inputs, same bytes moved, same results.
+      whole batch on `mojo` tensors, every copy and kernel on one stream;
+    * ``pipelined``: ``torch_mojo_backend_b200.HostAttentionPipeline`` - the batch cut into
+      pieces of whole (batch entry, kv-head group) units that go through the two registered
+      flash operators with uploads, kernels and downloads on three streams.  Same inputs, same
+      bytes moved, bitwise the same results (checked here before timing).
+
+    ``value`` is the pipelined number when the step is large enough to repay the pipelining
+    (more than one piece), else the single call.
     """
     import torch_mojo_backend_b200 as tmb
-    from oracle import sdpa_oracle as O
 
     tmb.register_mojo_devices()
     torch.mojo.set_device(local)
-    cpu_inputs = O.make_inputs(cfg, seed=rank)
     host = []
-    for t in cpu_inputs:
+    for t in (q_dev, k_dev, v_dev, dout_dev):
         p = tmb.pinned_empty(t.shape, t.dtype)
-        p.copy_(t)
+        p.copy_(t.cpu())
         host.append(p)
     hq, hk, hv, hdo = host
     steps = max(1, min(args.steps, 5))
@@ -326,11 +438,11 @@ def run_e2e(cfg, rank, world, local, args):
     h2d = sum(t.numel() * t.element_size() for t in ((hq, hk, hv, hdo) if cfg.backward else (hq, hk, hv)))
     # results land in pre-pinned host buffers: out, and dq/dk/dv when the config has a backward
     res_out = tmb.pinned_empty(hq.shape, hq.dtype)
-    res_grads = [tmb.pinned_empty(t.shape, t.dtype) for t in (hq, hk, hv)] if cfg.backward else []
-    d2h = sum(t.numel() * t.element_size() for t in [res_out] + res_grads)
+    res_grads = tuple(tmb.pinned_empty(t.shape, t.dtype) for t in (hq, hk, hv)) if cfg.backward else None
+    d2h = sum(t.numel() * t.element_size() for t in (res_out,) + (res_grads or ()))
     dev = torch.device("mojo", local)
 
-    def step():
+    def single_call():
         q = hq.to(dev, non_blocking=True)
         k = hk.to(dev, non_blocking=True)
         v = hv.to(dev, non_blocking=True)
@@ -345,61 +457,16 @@ def run_e2e(cfg, rank, world, local, args):
             out.backward(do)
             for dst, t in zip(res_grads, (q, k, v)):
                 dst.copy_(t.grad, non_blocking=True)
-        return res_out
 
-    # ---- pipelined over the batch entries: three streams, events between them
-    main = torch.cuda.current_stream(local)
-    s_in, s_run, s_out = (torch.cuda.Stream(device=local) for _ in range(3))
-    flash_fwd = torch.ops.aten._scaled_dot_product_flash_attention
-    flash_bwd = torch.ops.aten._scaled_dot_product_flash_attention_backward
+    pipe = tmb.HostAttentionPipeline(local)
+    n_pieces = len(pipe.pieces(hq, hk, cfg.backward))
 
-    # pieces: contiguous blocks of the host buffers, about 40 MB of upload each (smaller ones
-    # cost more in host-side dispatch than the overlap wins) - ranges of batch entries, or, when
-    # a single batch entry is larger than that, its kv heads in two groups (never cutting a GQA
-    # group)
-    rep_q = cfg.Hq // cfg.Hkv
-    wanted = max(1, min(2 * cfg.B, h2d // (40 << 20)))
-    if wanted <= cfg.B:
-        bounds = [round(n * cfg.B / wanted) for n in range(wanted + 1)]
-        pieces = [(slice(a, b), (slice(None), slice(None))) for a, b in zip(bounds, bounds[1:]) if b > a]
-    else:
-        split = 2 if cfg.Hkv % 2 == 0 else 1
-        pieces = [(slice(i, i + 1), (slice(g * cfg.Hkv // split * rep_q, (g + 1) * cfg.Hkv // split * rep_q),
-                                     slice(g * cfg.Hkv // split, (g + 1) * cfg.Hkv // split)))
-                  for i in range(cfg.B) for g in range(split)]
-
-    def step_pipelined(keep):
-        """`keep` collects every device tensor of the step: the three streams use one another's
-        allocations, so nothing may go back to the allocator before the final synchronisation."""
-        for s in (s_in, s_run, s_out):
-            s.wait_stream(main)
-        for i, (qs, ks) in pieces:
-            with torch.cuda.stream(s_in):
-                dq_in = [hq[i, qs].to(dev, non_blocking=True), hk[i, ks].to(dev, non_blocking=True),
-                         hv[i, ks].to(dev, non_blocking=True)]
-                if cfg.backward:
-                    dq_in.append(hdo[i, qs].to(dev, non_blocking=True))
-                uploaded = torch.cuda.Event()
-                uploaded.record(s_in)
-            with torch.cuda.stream(s_run):
-                s_run.wait_event(uploaded)
-                fwd = flash_fwd(dq_in[0], dq_in[1], dq_in[2], 0.0, cfg.causal, False, scale=cfg.scale)
-                out, lse = fwd[0], fwd[1]
-                grads = ()
-                if cfg.backward:
-                    grads = flash_bwd(dq_in[3], dq_in[0], dq_in[1], dq_in[2], out, lse, None, None, fwd[4], fwd[5],
-                                      0.0, cfg.causal, fwd[6], fwd[7], scale=cfg.scale)
-                computed = torch.cuda.Event()
-                computed.record(s_run)
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(computed)
-                res_out[i, qs].copy_(out, non_blocking=True)
-                for dst, g, hs in zip(res_grads, grads, (qs, ks, ks)):
-                    dst[i, hs].copy_(g, non_blocking=True)
-            keep.extend(dq_in)
-            keep.extend((out, lse) + tuple(grads))
-        for s in (s_in, s_run, s_out):
-            main.wait_stream(s)
+    def pipelined():
+        pipe.run(hq, hk, hv, hdo if cfg.backward else None, is_causal=cfg.causal, scale=cfg.scale, out=res_out,
+                 grads=res_grads)
+        # the host reads the results after every step anyway; once the step has drained, its
+        # device tensors go back to the allocator, so every step reuses the same blocks
+        pipe.synchronize()
 
     def time_steps(fn):
         barrier(world)
@@ -413,47 +480,41 @@ def run_e2e(cfg, rank, world, local, args):
 
     flops = cfg.fwd_flops() + (cfg.bwd_flops() if cfg.backward else 0.0)
     for _ in range(2):
-        step()
-    ms_single = time_steps(step)
-    # the pipelined walk must reproduce the single call bit for bit before it is timed
+        single_call()
+    ms_single = time_steps(single_call)
     torch.cuda.synchronize()
-    ref = [res_out.clone()] + [g.clone() for g in res_grads]
-    for t in [res_out] + res_grads:
+    ref = [res_out.clone()] + [g.clone() for g in (res_grads or ())]
+    for t in (res_out,) + (res_grads or ()):
         t.zero_()
-    keep = []
-    step_pipelined(keep)
-    torch.cuda.synchronize()
-    same = all(torch.equal(a, b) for a, b in zip(ref, [res_out] + res_grads))
-    step_pipelined(keep)
-    torch.cuda.synchronize()
-    keep.clear()
-
-    def pipelined_and_release():
-        # the host reads the results after every step anyway; once the step has drained, its
-        # device tensors go back to the allocator, so every step reuses the same blocks
-        step_pipelined(keep)
-        main.synchronize()
-        keep.clear()
-
-    ms_pipe = time_steps(pipelined_and_release)
+    pipelined()
+    same = all(torch.equal(a, b) for a, b in zip(ref, (res_out,) + (res_grads or ())))
+    pipelined()
+    ms_pipe = time_steps(pipelined)
     tf = lambda ms: round(world * flops / (ms * 1e-3) / 1e12, 2)
-    pipelined = {"value": tf(ms_pipe), "ms_per_step": round(ms_pipe, 3), "pieces": len(pieces),
-                 "matches_single_call_bitwise": bool(same),
-                 "api": "aten::_scaled_dot_product_flash_attention + _backward on mojo tensors, the batch in "
-                        f"{len(pieces)} contiguous pieces; uploads, kernels and downloads on three streams"}
-    single = {"value": tf(ms_single), "ms_per_step": round(ms_single, 3),
-              "api": "F.scaled_dot_product_attention + backward over the whole batch, one stream"}
-    # both are the public operator API with pinned host buffers in and out; the headline is the
-    # faster way of driving it for this workload (small steps do not repay the pipelining)
-    best_ms, mode = (ms_pipe, "pipelined") if ms_pipe <= ms_single else (ms_single, "single_call")
+    gbs = lambda nbytes, ms: round(nbytes / (ms * 1e-3) / 1e9, 2)
+    entry = lambda ms, api, extra: dict({"value": tf(ms), "ms_per_step": round(ms, 3), "api": api,
+                                         "h2d_gbs_per_gpu": gbs(h2d, ms), "d2h_gbs_per_gpu": gbs(d2h, ms)}, **extra)
+    single = entry(ms_single, "F.scaled_dot_product_attention + backward on mojo tensors, whole batch, one stream", {})
+    piped = entry(ms_pipe, "torch_mojo_backend_b200.HostAttentionPipeline: the batch in pieces; uploads, kernels and "
+                           "downloads on three streams", {"pieces": n_pieces, "matches_single_call_bitwise": bool(same)})
+    use_pipe = n_pieces > 1 and same
+    best_ms, mode = (ms_pipe, "pipelined") if use_pipe else (ms_single, "single_call")
+    try:
+        cores = sorted(os.sched_getaffinity(0))
+    except (AttributeError, OSError):
+        cores = []
     return {"value": tf(best_ms), "unit": "TFLOP/s", "ms_per_step": round(best_ms, 3), "steps": steps,
             "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "mode": mode,
-            "pipelined": pipelined, "single_call": single}
+            "h2d_gbs_per_gpu": gbs(h2d, best_ms), "d2h_gbs_per_gpu": gbs(d2h, best_ms),
+            "bound": "host link: the step moves h2d + d2h bytes over PCIe around a few ms of kernels; with several "
+                     "ranks on one host the copies of all ranks share the host's memory and PCIe fabric",
+            "host_cores_of_this_rank": len(cores), "ranks_on_host": world,
+            "pipelined": piped, "single_call": single}
 
 
 def run_reference(args):
     """The reference arm: the reference's own path cannot be built here (it needs the Mojo
-    toolchain), so — as its tests do — torch's CPU SDPA stands in, timed on all host cores on a
+    toolchain), so - as its tests do - torch's CPU SDPA stands in, timed on all host cores on a
     bounded slice of the same workload.  Only rank 0 works."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -471,11 +532,14 @@ def run_reference(args):
             secs_all.append(secs)
     value = statistics.median(vals)
     line = {
-        "impl": "reference", "metric": METRIC, "value": round(value, 4), "unit": "TFLOP/s",
+        "impl": "reference", "metric": metric_name(cfg), "value": round(value, 4), "unit": "TFLOP/s",
         "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(1e3 * statistics.median(secs_all), 2), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": str(cfg.dtype).replace("torch.", ""), "data": "synthetic",
-        "config": {"workload": f"{cfg.name} (CPU slice: {sample})"},
+        "config": {"workload": f"{cfg.name}: {'causal' if cfg.causal else 'non-causal'} "
+                               f"{'fwd+bwd' if cfg.backward else 'fwd'} B={cfg.B} Hq={cfg.Hq} Hkv={cfg.Hkv} S={cfg.S} "
+                               f"D={cfg.D} per GPU",
+                   "cpu_sample": sample},
         "cpu_baseline": {"value": round(value, 4), "unit": "TFLOP/s", "cores": threads, "kind": "port",
                          "sample": sample},
         "e2e": {"value": round(value, 4), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -491,6 +555,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--config", default="C3", choices=["C1", "C2", "C3", "C4", "C5"])
+    ap.add_argument("--scaling", default="auto", choices=["auto", "weak", "strong"],
+                    help="N > 1: weak = a full per-GPU problem on every rank; strong = one problem split over the "
+                         "ranks, gathered and validated (auto: strong for C4 and C5)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-sample-heads", type=int, default=0,
                     help="KV-head groups of one batch entry in the CPU sample (0: sized to about 2 TFLOP a repetition)")

@@ -38,6 +38,24 @@ def load_golden(name):
     return meta, q, k, v, dout, expected
 
 
+def parity_report(name, got, ref, tol, dtype=None):
+    """Both bounds of the parity contract for one tensor, as numbers:
+    ``max_abs`` - the strict max-abs error; ``over_flat`` - how many elements exceed the flat
+    tolerance `tol`; ``over_widened`` - how many exceed `tol` + half a storage ulp of the
+    reference value (the bound `assert_within` enforces); ``n`` - elements compared."""
+    got = got.detach().float().cpu()
+    ref = ref.detach().float().cpu()
+    finite = torch.isfinite(ref)
+    # entries that are -inf / +inf on both sides (logsumexp of a row that sees no key) agree exactly
+    same_inf = (~finite) & (got == ref)
+    err = torch.where(finite, (got - ref).abs(), torch.where(same_inf, torch.zeros_like(ref), torch.full_like(ref, float("inf"))))
+    half_ulp = {torch.bfloat16: 2.0 ** -8, torch.float16: 2.0 ** -11}.get(dtype, 0.0)
+    bound = tol + half_ulp * torch.where(finite, ref.abs(), torch.zeros_like(ref))
+    return {"name": name, "max_abs": err.max().item(), "over_flat": int((err > tol).sum()),
+            "over_widened": int((err > bound).sum()), "n": err.numel(), "tol": tol,
+            "max_ref": ref[finite].abs().max().item() if finite.any() else 0.0}
+
+
 def assert_within(name, got, ref, tol, dtype=None):
     """max-abs `tol`, widened by half a bf16/fp16 ulp of the reference value where the reference
     is large enough that rounding the result to the storage type alone exceeds `tol` (half an

@@ -33,6 +33,19 @@ def test_reference_arm_prints_one_contract_line():
     assert rec["e2e"] == {"value": rec["value"], "unit": rec["unit"], "h2d_bytes_per_step": 0,
                           "d2h_bytes_per_step": 0}
     assert "workload" in rec["config"]
+    # the metric names the configuration's own dtype and mask
+    assert rec["metric"] == "flash-attn fwd+bwd TFLOP/s (bf16, causal)"
+
+
+def test_metric_label_follows_the_configuration():
+    sys.path.insert(0, ROOT)
+    import bench
+    from oracle import sdpa_oracle as O
+
+    assert bench.metric_name(O.CONFIGS["C1"]) == "flash-attn fwd TFLOP/s (fp32, causal)"
+    assert bench.metric_name(O.CONFIGS["C3"]) == "flash-attn fwd+bwd TFLOP/s (bf16, causal)"
+    assert bench.metric_name(O.CONFIGS["C4"]) == "flash-attn fwd TFLOP/s (bf16, causal)"
+    assert bench.metric_name(O.CONFIGS["C5"]) == "flash-attn fwd+bwd TFLOP/s (fp16, non-causal)"
 
 
 def test_reference_arm_other_ranks_exit_without_work():

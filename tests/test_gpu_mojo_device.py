@@ -103,3 +103,35 @@ def test_zero_copy_interop_with_cuda_tensors(mojo_registered):
     back = torch.from_dlpack(m)
     assert back.data_ptr() == x.data_ptr()
     assert mojo_registered.to_cuda(m.transpose(0, 1)).data_ptr() == x.data_ptr()
+
+
+def test_host_attention_pipeline_is_bitwise_the_single_call(mojo_registered):
+    """The package's host-tensor entry point: the batch in pieces over three streams gives the
+    bits of one F.scaled_dot_product_attention + backward over the whole batch."""
+    import torch_mojo_backend_b200 as tmb
+
+    B, Hq, Hkv, S, D = 6, 8, 2, 512, 128
+    g = torch.Generator().manual_seed(21)
+    host = [tmb.pinned_empty(shape, torch.bfloat16) for shape in
+            ((B, Hq, S, D), (B, Hkv, S, D), (B, Hkv, S, D), (B, Hq, S, D))]
+    for t in host:
+        t.copy_((torch.randn(t.shape, generator=g) * 0.5).to(torch.bfloat16))
+    hq, hk, hv, hdo = host
+    mq, mk, mv = (t.to("mojo").requires_grad_() for t in (hq, hk, hv))
+    out = torch.nn.functional.scaled_dot_product_attention(mq, mk, mv, is_causal=True, enable_gqa=True)
+    out.backward(hdo.to("mojo"))
+    torch.mojo.synchronize()
+    pipe = tmb.HostAttentionPipeline(0, piece_bytes=4 << 20)   # small pieces: several per pass
+    assert len(pipe.pieces(hq, hk, True)) > 1
+    for _ in range(2):   # twice: result buffers and streams are reused
+        res_out, grads = pipe.run(hq, hk, hv, hdo, is_causal=True)
+        pipe.synchronize()
+        assert torch.equal(res_out, out.detach().cpu())
+        assert torch.equal(grads[0], mq.grad.cpu()) and torch.equal(grads[1], mk.grad.cpu())
+        assert torch.equal(grads[2], mv.grad.cpu())
+    # forward only, one batch entry larger than a piece: its kv-head groups are the pieces
+    pipe2 = tmb.HostAttentionPipeline(0, piece_bytes=1 << 20)
+    assert len(pipe2.pieces(hq, hk, False)) == 2 * B
+    res_out, grads = pipe2.run(hq, hk, hv, None, is_causal=True)
+    pipe2.synchronize()
+    assert grads is None and torch.equal(res_out, out.detach().cpu())

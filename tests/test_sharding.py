@@ -31,6 +31,32 @@ def test_shard_never_splits_a_gqa_group():
         O.shard(O.CONFIGS["C3"], 0, 3)
 
 
+def test_bench_shard_slices_tile_the_problem_and_agree_with_the_config_shards():
+    """bench.py's strong-scaling split: the ranks' (batch, head) slices are disjoint, cover the
+    problem, never cut a GQA group and have the shape oracle.shard() names."""
+    sys.path.insert(0, ROOT)
+    import bench
+
+    for name, worlds in (("C4", (2, 4, 8)), ("C5", (2, 4, 8)), ("C3", (2, 4, 8, 16, 32)), ("C2", (2, 4, 8))):
+        cfg = O.CONFIGS[name]
+        group = cfg.Hq // cfg.Hkv
+        for world in worlds:
+            seen_q = torch.zeros(cfg.B, cfg.Hq, dtype=torch.int32)
+            seen_k = torch.zeros(cfg.B, cfg.Hkv, dtype=torch.int32)
+            for rank in range(world):
+                bs, qs, ks = bench.shard_slices(cfg, rank, world)
+                seen_q[bs, qs] += 1
+                seen_k[bs, ks] += 1
+                part = O.shard(cfg, rank, world)
+                assert seen_q[bs, qs].shape == (part.B, part.Hq) and seen_k[bs, ks].shape == (part.B, part.Hkv)
+                q_heads = torch.arange(cfg.Hq)[qs]
+                k_heads = torch.arange(cfg.Hkv)[ks]
+                assert torch.equal(q_heads // group, k_heads.repeat_interleave(group))
+            assert torch.all(seen_q == 1) and torch.all(seen_k == 1)
+    with pytest.raises(ValueError):
+        bench.shard_slices(O.CONFIGS["C3"], 0, 3)
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))

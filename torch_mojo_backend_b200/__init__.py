@@ -51,4 +51,12 @@ def to_cuda(t) -> torch.Tensor:
     return t._cuda_view()
 
 
-__all__ = ["register_mojo_devices", "from_cuda", "to_cuda", "pinned_empty"]
+def __getattr__(name):
+    if name == "HostAttentionPipeline":
+        from .host_pipeline import HostAttentionPipeline
+
+        return HostAttentionPipeline
+    raise AttributeError(name)
+
+
+__all__ = ["register_mojo_devices", "from_cuda", "to_cuda", "pinned_empty", "HostAttentionPipeline"]

@@ -403,7 +403,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
     }
   } else if (warp < 12) {
     // =========================== correction warps ===========================
-    reg_dealloc<104>();
+    reg_dealloc<96>();
     const int row = threadIdx.x & 127;
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
     uint32_t n_msg[2] = {0, 0};   // messages read so far, per tile
@@ -518,10 +518,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
     }
     // the staged output tile must have been read before shared memory is given back
     if (warp == 8 && lane == 0 && store_pending) tma_store_wait_read();
-  } else if (warp == 15) {
-    reg_dealloc<24>();   // idle: it only donates registers
   } else {
-    reg_dealloc<88>();
+    // (all four warps of a warpgroup have to name the same register count)
+    reg_dealloc<80>();
     if (warp == 12 || warp == 13) {
       // =========================== MMA issuers (one per query tile) ===========================
       // A tcgen05.mma only issues once the tensor pipe has room, so the issuing lane is stalled

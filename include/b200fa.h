@@ -103,9 +103,10 @@ size_t b200fa_bwd_workspace_bytes(int64_t batch, int64_t heads_q, int64_t heads_
  * needs on `stream`).
  * Everything is ordered on `stream`: work enqueued before the call is seen, work enqueued
  * after it sees dq, dk and dv.  For causal 16-bit problems one of the kernels runs on a side
- * stream the library keeps per host thread and device, forked from and joined back into
- * `stream` with events (this also works inside stream capture); the side stream and its two
- * events are created at the first such call of a thread, so make that call outside capture.
+ * stream of a small per-device pool the library keeps (picked by the value of `stream`), forked
+ * from and joined back into `stream` with events (this also works inside stream capture); a
+ * side stream and its two events are created at the first call that picks them, so make that
+ * call outside capture.
  * Replaces flash_attention_bwd_<dtype>_d<D>_causal{,_strided_qkv}
  * (torch_mojo_backend/eager_flash_attention/fa4_ops.mojo:158-226).
  */

@@ -9,6 +9,12 @@ on seeded inputs.  The cases reuse the reference tests' seeds, shapes and input 
 ``grad_output = randn``; :9609-9683 and :9697-9775: BHSD and partial-tail shapes with seeds
 ``20260816 + S`` / ``20260817 + S``), kept small so each file is a few hundred KB.
 Inputs are stored already rounded to the case dtype (as fp32 arrays); outputs are fp32.
+
+The ``ext_*`` fixtures cover what lies beyond the reference's gate: a causal mask over unequal
+lengths in both alignments (top-left: torch's rule; bottom-right: fa4_fwd_kernel.mojo:266-273)
+and dropout.  Their expected values come from the float64 restatement (oracle/restatement.py),
+the dropout mask from the numpy Philox4x32-10 (oracle/philox.py), stored bit-packed, so the
+torch-side oracle, the mask generator and the kernels are all pinned against them.
 """
 
 import os
@@ -68,6 +74,35 @@ def main():
         cases[name] = dict(q=q.float().numpy(), k=k.float().numpy(), v=v.float().numpy(), dout=dout.float().numpy(),
                            out=out.numpy(), lse=lse.numpy(), dq=dq.numpy(), dk=dk.numpy(), dv=dv.numpy(),
                            meta=np.array([b, hq, hkv, s, d, int(causal), code]))
+    from oracle import restatement as R
+    from oracle.philox import keep_mask
+
+    # name, seed, b, hq, hkv, sq, sk, d, mode, dtype, (p, philox seed, philox offset)
+    for name, seed, b, hq, hkv, sq, sk, d, mode, dtype, drop in (
+        ("ext_bottom_right_bf16", 20260920, 1, 4, 2, 96, 200, 64, 2, torch.bfloat16, None),
+        ("ext_top_left_f16", 20260921, 1, 2, 2, 200, 96, 128, 1, torch.float16, None),
+        ("ext_more_queries_than_keys_bf16", 20260922, 1, 2, 1, 160, 72, 64, 2, torch.bfloat16, None),
+        ("ext_dropout_bf16", 20260923, 2, 2, 1, 130, 130, 64, 1, torch.bfloat16, (0.25, 0x0123456789ABCDEF, 40)),
+    ):
+        g = torch.Generator().manual_seed(seed)
+        q = (torch.randn(b, hq, sq, d, generator=g) * 0.5).to(dtype)
+        k = (torch.randn(b, hkv, sk, d, generator=g) * 0.5).to(dtype)
+        v = (torch.randn(b, hkv, sk, d, generator=g) * 0.5).to(dtype)
+        dout = torch.randn(b, hq, sq, d, generator=g).to(dtype)
+        f64 = lambda t: t.float().numpy().astype(np.float64)
+        keep, keep_scale = (None, 1.0) if drop is None else keep_mask(b, hq, sq, sk, *drop)
+        out, lse = R.forward(f64(q), f64(k), f64(v), mode, d ** -0.5, keep, keep_scale)
+        dq, dk, dv = R.backward(f64(q), f64(k), f64(v), f64(dout), mode, d ** -0.5, keep, keep_scale)
+        code = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}[dtype]
+        arrays = dict(q=q.float().numpy(), k=k.float().numpy(), v=v.float().numpy(), dout=dout.float().numpy(),
+                      out=out.astype(np.float32), lse=lse.astype(np.float32), dq=dq.astype(np.float32),
+                      dk=dk.astype(np.float32), dv=dv.astype(np.float32),
+                      meta=np.array([b, hq, hkv, sq, sk, d, mode, code]))
+        if drop is not None:
+            arrays["keep_bits"] = np.packbits(keep)
+            arrays["drop"] = np.array([int(round(drop[0] * 1e6)), drop[1] & 0xFFFFFFFF, drop[1] >> 32, drop[2]],
+                                      dtype=np.uint64)
+        cases[name] = arrays
     for name, arrays in cases.items():
         np.savez_compressed(os.path.join(HERE, name + ".npz"), **{k: np.asarray(v) for k, v in arrays.items()})
         print(name, {k: tuple(np.asarray(v).shape) for k, v in arrays.items()})

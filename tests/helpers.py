@@ -17,7 +17,32 @@ TOL_LSE = 1e-3
 
 
 def golden_names():
-    return sorted(os.path.splitext(os.path.basename(p))[0] for p in glob.glob(os.path.join(GOLDEN_DIR, "*.npz")))
+    """The fixtures inside the reference's gate (equal lengths, no dropout)."""
+    names = sorted(os.path.splitext(os.path.basename(p))[0] for p in glob.glob(os.path.join(GOLDEN_DIR, "*.npz")))
+    return [n for n in names if not n.startswith("ext_")]
+
+
+def ext_golden_names():
+    """The fixtures beyond it: causal masks over unequal lengths, dropout."""
+    names = sorted(os.path.splitext(os.path.basename(p))[0] for p in glob.glob(os.path.join(GOLDEN_DIR, "ext_*.npz")))
+    return names
+
+
+def load_ext_golden(name):
+    """Returns (meta dict, q, k, v, dout as CPU tensors of the case dtype, expected fp32 dict).
+    meta: B, Hq, Hkv, Sq, Sk, D, mode (B200FA_CAUSAL_*), dtype, scale, dropout (None or
+    (p, seed, offset)), keep (bool array (B,Hq,Sq,Sk) or None)."""
+    z = np.load(os.path.join(GOLDEN_DIR, name + ".npz"))
+    b, hq, hkv, sq, sk, d, mode, code = (int(x) for x in z["meta"])
+    dtype = DTYPES[code]
+    meta = dict(B=b, Hq=hq, Hkv=hkv, Sq=sq, Sk=sk, D=d, mode=mode, dtype=dtype, scale=d ** -0.5, dropout=None, keep=None)
+    if "drop" in z:
+        p6, lo, hi, off = (int(x) for x in z["drop"])
+        meta["dropout"] = (p6 / 1e6, lo | (hi << 32), off)
+        meta["keep"] = np.unpackbits(z["keep_bits"])[: b * hq * sq * sk].reshape(b, hq, sq, sk).astype(bool)
+    q, k, v, dout = (torch.from_numpy(z[n]).to(dtype) for n in ("q", "k", "v", "dout"))
+    expected = {n: torch.from_numpy(z[n]) for n in ("out", "lse", "dq", "dk", "dv")}
+    return meta, q, k, v, dout, expected
 
 
 def load_golden(name):

@@ -893,10 +893,10 @@ SideStream* side_stream_for(int dev, cudaStream_t caller) {
 }
 
 // cudaFuncSetAttribute for one kernel, once per device, safe against concurrent first calls.
+// `once` and `result` belong to the kernel (the caller keeps them as statics of the function
+// template that names it: kernels of the same signature must not share them).
 template <typename Kernel>
-cudaError_t allow_dynamic_smem(Kernel kern, int bytes) {
-  static std::once_flag once[64];
-  static cudaError_t result[64];
+cudaError_t allow_dynamic_smem(Kernel kern, int bytes, std::once_flag (&once)[64], cudaError_t (&result)[64]) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
@@ -915,8 +915,10 @@ cudaError_t launch_one(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
   cudaError_t e = cudaSuccess;
   auto k1 = bwd_dkdv_kernel<kD, kBf16, kCausal, kDropout>;
   auto k2 = bwd_dq_kernel<kD, kBf16, kCausal, kDropout>;
-  if ((e = allow_dynamic_smem(k1, Cfg::kSmemBytes)) != cudaSuccess) return e;
-  if ((e = allow_dynamic_smem(k2, Cfg::kSmemBytes)) != cudaSuccess) return e;
+  static std::once_flag once1[64], once2[64];
+  static cudaError_t result1[64], result2[64];
+  if ((e = allow_dynamic_smem(k1, Cfg::kSmemBytes, once1, result1)) != cudaSuccess) return e;
+  if ((e = allow_dynamic_smem(k2, Cfg::kSmemBytes, once2, result2)) != cudaSuccess) return e;
   if (p.parts & 1) {
     constexpr int kRowsPerWarp = 32 / (kD / 8);
     const int64_t total_rows = static_cast<int64_t>(p.B) * p.Hq * p.Spad;

@@ -50,6 +50,9 @@ constexpr int kEmuOf8 = B200FA_EMU_OF8;
 // 2^x for x <= ~127 on the FMA pipe, two values at a time: x = n + f with n = floor(x),
 // 2^f by a cubic fitted on [0,1) (max relative error 8.7e-5, far below 16-bit rounding of
 // P), and n added straight into the exponent field.
+#ifdef B200FA_X_NOFMAX3
+#define fmax3(a, b, c) fmaxf(fmaxf((a), (b)), (c))
+#endif
 __device__ __forceinline__ float2 exp2_emulated2(float2 x) {
   const float kMagic = 12582912.f;  // 1.5 * 2^23: x + kMagic (rounded down) holds floor(x) in its low mantissa bits
   x.x = fmaxf(x.x, -126.f);
@@ -356,6 +359,27 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
         // until the next quarter's exponentials have been issued, and the MMA lane is told about
         // a half (two quarters) at a time: P V starts on the first half while the second is
         // still being exponentiated.
+#ifdef B200FA_X_HALVES
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+#pragma unroll
+          for (int i = half * 32; i < half * 32 + 32; ++i) {
+            const float2 x = __ffma2_rn(make_float2(sf[2 * i], sf[2 * i + 1]), c2, nmc2);
+            float2 pv;
+            if ((i & 7) < kEmuOf8) {
+              pv = exp2_emulated2(x);
+            } else {
+              pv = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+            }
+            if (i & 1) rsb = __fadd2_rn(rsb, pv); else rsa = __fadd2_rn(rsa, pv);
+            pk[i] = pack2<kBf16>(pv.x, pv.y);
+          }
+          tmem_st32(tS + half * 32, pk + half * 32);
+          tmem_wait_st();
+          tc_fence_before();
+          mbar_arrive_warp(&p_full[t * 2 + half]);
+        }
+#else
 #pragma unroll
         for (int qt = 0; qt < 4; ++qt) {
 #pragma unroll
@@ -387,6 +411,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive_warp(&p_full[t * 2 + 1]);
+#endif
         l = l * sc + ((rsa.x + rsa.y) + (rsb.x + rsb.y));
         ++n_s;
       }
@@ -707,10 +732,10 @@ teardown:
 }
 
 // cudaFuncSetAttribute for one kernel, once per device, safe against concurrent first calls.
+// `once` and `result` belong to the kernel (the caller keeps them as statics of the function
+// template that names it: kernels of the same signature must not share them).
 template <typename Kernel>
-cudaError_t allow_dynamic_smem(Kernel kern, int bytes) {
-  static std::once_flag once[64];
-  static cudaError_t result[64];
+cudaError_t allow_dynamic_smem(Kernel kern, int bytes, std::once_flag (&once)[64], cudaError_t (&result)[64]) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
@@ -726,7 +751,9 @@ cudaError_t launch_one(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
                        const FwdParams& p, const FwdSched& sched, cudaStream_t stream) {
   using Cfg = FwdCfg<kD>;
   auto kern = fwd_kernel<kD, kBf16, kCausal, kDropout>;
-  cudaError_t e = allow_dynamic_smem(kern, Cfg::kSmemBytes);
+  static std::once_flag once[64];
+  static cudaError_t result[64];
+  cudaError_t e = allow_dynamic_smem(kern, Cfg::kSmemBytes, once, result);
   if (e != cudaSuccess) return e;
   int grid = sched.total_items;
   if (sched.mode == kSchedStride) {

@@ -63,11 +63,12 @@ def load_golden(name):
     return meta, q, k, v, dout, expected
 
 
-def parity_report(name, got, ref, tol, dtype=None):
+def parity_report(name, got, ref, tol, dtype=None, ref_is_rounded=False):
     """Both bounds of the parity contract for one tensor, as numbers:
     ``max_abs`` - the strict max-abs error; ``over_flat`` - how many elements exceed the flat
     tolerance `tol`; ``over_widened`` - how many exceed `tol` + half a storage ulp of the
-    reference value (the bound `assert_within` enforces); ``n`` - elements compared."""
+    reference value (the bound `assert_within` enforces; a whole ulp when the reference is itself
+    a result rounded to the 16-bit storage type); ``n`` - elements compared."""
     got = got.detach().float().cpu()
     ref = ref.detach().float().cpu()
     finite = torch.isfinite(ref)
@@ -75,6 +76,8 @@ def parity_report(name, got, ref, tol, dtype=None):
     same_inf = (~finite) & (got == ref)
     err = torch.where(finite, (got - ref).abs(), torch.where(same_inf, torch.zeros_like(ref), torch.full_like(ref, float("inf"))))
     half_ulp = {torch.bfloat16: 2.0 ** -8, torch.float16: 2.0 ** -11}.get(dtype, 0.0)
+    if ref_is_rounded:
+        half_ulp *= 2
     bound = tol + half_ulp * torch.where(finite, ref.abs(), torch.zeros_like(ref))
     return {"name": name, "max_abs": err.max().item(), "over_flat": int((err > tol).sum()),
             "over_widened": int((err > bound).sum()), "n": err.numel(), "tol": tol,

@@ -70,8 +70,10 @@ def test_cross_attention_through_sdpa_with_grad(mojo):
     assert tuple(km.grad.shape) == (2, 2, 777, 128)
     for name, got, ref in (("dq", qm.grad, rdq), ("dk", km.grad, rdk), ("dv", vm.grad, rdv)):
         assert_within(name, got.cpu(), ref, TOL_16BIT, torch.bfloat16)
-    with pytest.raises(NotImplementedError):
-        torch.nn.functional.scaled_dot_product_attention(qm, km, vm, is_causal=True, enable_gqa=True)
+    # is_causal over unequal lengths keeps torch's meaning: the diagonal starts at the top-left corner
+    ref_causal, _ = O.sdpa_forward(q, k, v, True, 128 ** -0.5)
+    out_causal = torch.nn.functional.scaled_dot_product_attention(qm, km, vm, is_causal=True, enable_gqa=True)
+    assert_within("causal out", out_causal.detach().cpu(), ref_causal, TOL_16BIT, torch.bfloat16)
 
 
 def test_autocast_block_runs_the_bf16_kernel(mojo):

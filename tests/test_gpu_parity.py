@@ -195,7 +195,7 @@ def test_config2_full_size_vs_oracle():
                        parity_report("lse", lse, ref_lse, TOL_LSE),
                        parity_report("dq", dq, rdq, TOL_16BIT, cfg.dtype),
                        parity_report("dk", dk, rdk, TOL_16BIT, cfg.dtype),
-                       parity_report("dv", dv, rdv, TOL_16BIT, cfg.dtype)], flat_fraction=1e-4)
+                       parity_report("dv", dv, rdv, TOL_16BIT, cfg.dtype)])
 
 
 def _report(cfg_name, rows):
@@ -215,24 +215,25 @@ def _report(cfg_name, rows):
                 f.write(json.dumps(dict(r, config=cfg_name)) + "\n")
 
 
-def _check_rows(cfg_name, rows, flat_fraction=0.0):
-    """The stated contract is a flat max-abs tolerance.  It must hold outright for out, lse and
-    dQ; for dK/dV, whose largest elements are large enough that rounding the result to 16 bits
-    alone can exceed 2e-2, at most `flat_fraction` of the elements may exceed it and none may
-    exceed the bound widened by half a storage ulp of the reference."""
+def _check_rows(cfg_name, rows):
+    """Against the oracle the stated contract must hold as stated: a flat max-abs tolerance, no
+    element over it.  The on-device cross-check compares two results that were BOTH rounded to the
+    16-bit storage type, so neighbouring roundings of a large dV element differ by a whole ulp
+    (0.0625 at magnitude 8 in bf16): there the bound is the tolerance plus one storage ulp of the
+    reference, and the elements over the flat tolerance are only counted and printed."""
     _report(cfg_name, rows)
     for r in rows:
         assert r["over_widened"] == 0, r
-        allowed = flat_fraction * r["n"] if r["name"].split()[0] in ("dk", "dv") else 0
-        assert r["over_flat"] <= allowed, r
+        if not r["name"].endswith("vs simt"):
+            assert r["over_flat"] == 0, r
 
 
 @pytest.mark.parametrize("name", ["C2", "C3", "C4", "C5"])
 def test_full_size_configs_every_element_vs_exact_fp32_kernels_and_a_slice_vs_oracle(name):
     """The four 16-bit benchmark configurations at their real sizes (C4 at S = 32768, C3 and C5
     at their full batch x heads): every element of out / lse / dQ / dK / dV against the
-    exact-fp32 SIMT kernels on the device, and one (batch entry, kv-head group) at the full
-    sequence length against the CPU oracle."""
+    exact-fp32 SIMT kernels on the device, and against the CPU oracle everything (C2, C3), the
+    last two batch entries (C5) or the last head at the full 32768 rows (C4)."""
     from tests.helpers import parity_report
 
     cfg = O.CONFIGS[name]
@@ -240,25 +241,26 @@ def test_full_size_configs_every_element_vs_exact_fp32_kernels_and_a_slice_vs_or
     q, k, v, dout = O.make_inputs(cfg, seed=0)
     out, lse, dq, dk, dv = run_gpu(q, k, v, dout, cfg.causal, cfg.scale, backward=cfg.backward)
     s_out, s_lse, s_dq, s_dk, s_dv = run_gpu(q, k, v, dout, cfg.causal, cfg.scale, simt=True, backward=cfg.backward)
-    rows = [parity_report("out vs simt", out, s_out.float(), TOL_16BIT, cfg.dtype),
+    rows = [parity_report("out vs simt", out, s_out.float(), TOL_16BIT, cfg.dtype, True),
             parity_report("lse vs simt", lse, s_lse, TOL_LSE)]
     if cfg.backward:
-        rows += [parity_report("dq vs simt", dq, s_dq.float(), TOL_16BIT, cfg.dtype),
-                 parity_report("dk vs simt", dk, s_dk.float(), TOL_16BIT, cfg.dtype),
-                 parity_report("dv vs simt", dv, s_dv.float(), TOL_16BIT, cfg.dtype)]
-    # oracle: the last batch entry's last kv-head group (the heads farthest from the first work item)
-    b0, hk0 = cfg.B - 1, cfg.Hkv - 1
-    sl = slice(hk0 * group, (hk0 + 1) * group)
-    qs, ks, vs, ds = q[b0:b0 + 1, sl], k[b0:b0 + 1, hk0:hk0 + 1], v[b0:b0 + 1, hk0:hk0 + 1], dout[b0:b0 + 1, sl]
+        rows += [parity_report("dq vs simt", dq, s_dq.float(), TOL_16BIT, cfg.dtype, True),
+                 parity_report("dk vs simt", dk, s_dk.float(), TOL_16BIT, cfg.dtype, True),
+                 parity_report("dv vs simt", dv, s_dv.float(), TOL_16BIT, cfg.dtype, True)]
+    # oracle: C2 and C3 whole; C5 its last two batch entries; C4 its last head (S = 32768)
+    b0 = {"C5": cfg.B - 2}.get(name, 0)
+    hk0 = {"C4": cfg.Hkv - 1}.get(name, 0)
+    sl = slice(hk0 * group, cfg.Hq)
+    qs, ks, vs, ds = q[b0:, sl], k[b0:, hk0:], v[b0:, hk0:], dout[b0:, sl]
     ref_out, ref_lse = O.sdpa_forward(qs, ks, vs, cfg.causal, cfg.scale)
-    rows += [parity_report("out", out[b0:b0 + 1, sl], ref_out, TOL_16BIT, cfg.dtype),
-             parity_report("lse", lse[b0:b0 + 1, sl], ref_lse, TOL_LSE)]
+    rows += [parity_report("out", out[b0:, sl], ref_out, TOL_16BIT, cfg.dtype),
+             parity_report("lse", lse[b0:, sl], ref_lse, TOL_LSE)]
     if cfg.backward:
         _, rdq, rdk, rdv = O.sdpa_backward(qs, ks, vs, ds, cfg.causal, cfg.scale)
-        rows += [parity_report("dq", dq[b0:b0 + 1, sl], rdq, TOL_16BIT, cfg.dtype),
-                 parity_report("dk", dk[b0:b0 + 1, hk0:hk0 + 1], rdk, TOL_16BIT, cfg.dtype),
-                 parity_report("dv", dv[b0:b0 + 1, hk0:hk0 + 1], rdv, TOL_16BIT, cfg.dtype)]
-    _check_rows(name, rows, flat_fraction=1e-4)
+        rows += [parity_report("dq", dq[b0:, sl], rdq, TOL_16BIT, cfg.dtype),
+                 parity_report("dk", dk[b0:, hk0:], rdk, TOL_16BIT, cfg.dtype),
+                 parity_report("dv", dv[b0:, hk0:], rdv, TOL_16BIT, cfg.dtype)]
+    _check_rows(name, rows)
 
 
 @pytest.mark.parametrize("name", ["C2", "C3"])

@@ -58,6 +58,17 @@ def test_no_alloc_backward_matches_workspace_backward_twice_in_a_row():
         assert_within("dq", dq, ref_dq.float(), TOL_16BIT, q.dtype)
 
 
+def test_no_alloc_backward_serves_fp32_tensors_too():
+    """fp32 tensors go to the exact-fp32 kernels, which read the same two scratch arrays from the
+    built-in array (right after the 16-bit calls above have left their contents in it)."""
+    q, k, v, dout, out, lse = _case(3, 1, 4, 2, 200, 64, torch.float32, True)
+    ref_dq, ref_dk, ref_dv = raw.flash_bwd(dout, q, k, v, out, lse, causal=True)
+    before = _lib.launch_count()
+    dq, dk, dv = _no_alloc_backward(q, k, v, dout, out, lse, True)
+    assert _lib.launch_count() - before == 3
+    assert torch.equal(dq, ref_dq) and torch.equal(dk, ref_dk) and torch.equal(dv, ref_dv)
+
+
 def test_no_alloc_backward_refuses_problems_beyond_its_scratch():
     # 16 x 32 x 4096 rows need 16 MiB of scratch (> 8 MiB); never launched, so dummy pointers suffice
     big = _lib.Tensor4.make(0x7F0000000000, (16, 32, 4096, 128), (32 * 4096 * 128, 4096 * 128, 128, 1))

@@ -155,11 +155,6 @@ bool encode_map_16bit(CUtensorMap* map, const View4& t, int B, int H, int S, int
   return r == CUDA_SUCCESS;
 }
 
-int env_int(const char* name, int fallback) {
-  const char* v = std::getenv(name);
-  return (v && *v) ? std::atoi(v) : fallback;
-}
-
 namespace {
 
 // one warp waits, for `budget` SM cycles, on a barrier that nobody ever arrives at

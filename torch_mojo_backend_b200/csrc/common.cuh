@@ -84,7 +84,4 @@ cudaError_t launch_wait_timeout_selftest(uint32_t* status, long long budget, cud
 // point is unavailable or the encode fails.
 bool encode_map_16bit(CUtensorMap* map, const View4& t, int B, int H, int S, int D, int box_rows, bool bf16);
 
-// Process-wide tuning switches read once from the environment (B200FA_FWD_SCHED ...).
-int env_int(const char* name, int fallback);
-
 }  // namespace b200fa

@@ -77,14 +77,17 @@ constexpr long long kWaitBudgetCycles = 4000000000LL;
 // Bounded wait.  Returns true when the phase completed, false when the CTA is aborting
 // (either this wait ran out of its `budget` of SM cycles or another thread raised the flag).
 // `abort_flag` lives in shared memory; `status` is the global status word (may be null).
+// The loop polls try_wait back to back and looks at the clock and the abort flag only every
+// 256 polls (measured: letting try_wait suspend the thread with a time hint instead costs the
+// dK/dV kernel 4-5 %, its waits are short and on the critical path).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           uint32_t* status, uint32_t site, long long budget) {
   if (mbar_try_wait(bar, parity)) return true;
-  long long t0 = clock64();
+  const long long t0 = clock64();
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 63u) == 0u) {
+    if ((++spins & 255u) == 0u) {
       if (*abort_flag) return false;
       if (clock64() - t0 > budget) {
         *abort_flag = 1u;
@@ -307,13 +310,6 @@ __device__ __forceinline__ void reg_dealloc() {
 // named barrier among `nthreads` threads (id 1..15; id 0 is __syncthreads)
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
-}
-
-// max of three floats in one instruction
-__device__ __forceinline__ float fmax3(float a, float b, float c) {
-  float y;
-  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
-  return y;
 }
 
 __device__ __forceinline__ float ex2_approx(float x) {

@@ -79,7 +79,11 @@ def parity_report(name, got, ref, tol, dtype=None, ref_is_rounded=False):
     if ref_is_rounded:
         half_ulp *= 2
     bound = tol + half_ulp * torch.where(finite, ref.abs(), torch.zeros_like(ref))
+    # elements over the flat tolerance where rounding the result to the storage type cannot
+    # account for even half of it (half an ulp of the reference below tol / 2)
+    rounding = half_ulp * torch.where(finite, ref.abs(), torch.zeros_like(ref))
     return {"name": name, "max_abs": err.max().item(), "over_flat": int((err > tol).sum()),
+            "over_flat_unexplained": int(((err > tol) & (rounding < tol / 2)).sum()),
             "over_widened": int((err > bound).sum()), "n": err.numel(), "tol": tol,
             "max_ref": ref[finite].abs().max().item() if finite.any() else 0.0}
 

@@ -207,7 +207,8 @@ def _report(cfg_name, rows):
 
     for r in rows:
         print(f"parity {cfg_name:>3} {r['name']:<14} max_abs={r['max_abs']:.3e} over_flat_{r['tol']:g}={r['over_flat']}"
-              f"/{r['n']} over_widened={r['over_widened']} max|ref|={r['max_ref']:.2f}")
+              f"/{r['n']} (not explained by 16-bit rounding: {r['over_flat_unexplained']}) "
+              f"over_widened={r['over_widened']} max|ref|={r['max_ref']:.2f}")
     path = os.environ.get("B200FA_PARITY_REPORT")
     if path:
         with open(path, "a") as f:
@@ -216,15 +217,18 @@ def _report(cfg_name, rows):
 
 
 def _check_rows(cfg_name, rows):
-    """Against the oracle the stated contract must hold as stated: a flat max-abs tolerance, no
-    element over it.  The on-device cross-check compares two results that were BOTH rounded to the
-    16-bit storage type, so neighbouring roundings of a large dV element differ by a whole ulp
-    (0.0625 at magnitude 8 in bf16): there the bound is the tolerance plus one storage ulp of the
-    reference, and the elements over the flat tolerance are only counted and printed."""
+    """The stated contract is a flat max-abs tolerance (2e-2 on 16-bit tensors, 1e-3 on fp32 and
+    lse).  Every element must meet it, except where the 16-bit STORAGE makes that impossible for
+    any implementation: half a bf16 ulp is 0.0156 for 4 <= |x| < 8 and 0.031 for 8 <= |x| < 16, and
+    a few dV elements of the 4k-token GQA configuration are that large.  So: no element may exceed
+    the tolerance plus half a storage ulp of the reference (a whole ulp where the reference is
+    itself a 16-bit result of the exact-fp32 kernels), and no element may exceed the flat tolerance
+    unless rounding to the storage type accounts for at least half of it.  The counts are printed."""
     _report(cfg_name, rows)
     for r in rows:
         assert r["over_widened"] == 0, r
-        if not r["name"].endswith("vs simt"):
+        assert r["over_flat_unexplained"] == 0, r
+        if r["name"].split()[0] in ("out", "lse", "dq"):
             assert r["over_flat"] == 0, r
 
 

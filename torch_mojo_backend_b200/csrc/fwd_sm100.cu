@@ -10,8 +10,9 @@
 //
 //   warps 0-3   softmax of query tile 0   (thread i <-> TMEM lane i <-> query row i)
 //   warps 4-7   softmax of query tile 1
-//   warps 8-11  correction: rescale O in TMEM when a row max moved; epilogue: O / l staged in
-//               shared memory and written with TMA stores, LSE
+//   warps 8-11  epilogue: O / l staged in shared memory and written with TMA stores, LSE (the
+//               softmax warps rescale O themselves on the rare tile where a row max moved, so no
+//               KV step hands anything to these warps)
 //   warps 12-13 MMA issuers, one per query tile (one elected lane each issues tcgen05.mma / commit)
 //   warp  14    TMA producer (Q once, then a ring of K/V tiles)
 //   warp  15    idle (it only donates registers)
@@ -72,9 +73,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
   uint64_t* p_full = s_full + 2;                // [2 tiles][2 halves of the KV columns]
   uint64_t* o_full = p_full + 4;                // [2]
   uint64_t* o_ready = o_full + 2;               // [2]
-  uint64_t* sc_full = o_ready + 2;              // [2]
-  uint64_t* sc_empty = sc_full + 2;             // [2]
-  uint64_t* turn = sc_empty + 2;                // [2] MMA issuers' turn-taking
+  uint64_t* sc_full = o_ready + 2;              // [2] final row statistics (l, m) of a tile are in shared memory
+  uint64_t* turn = sc_full + 2;                 // [2] MMA issuers' turn-taking
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(turn + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -155,12 +155,11 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
     for (int t = 0; t < 2; ++t) {
       mbar_init(&s_full[t], 1);
       // fed by four warps each, one elected arrival per warp
-      mbar_init(&p_full[t * 2], 8);      // 4 softmax warps (P half 0) + 4 correction warps (O ready)
+      mbar_init(&p_full[t * 2], 4);      // the 4 softmax warps of the tile (P half 0 written, O rescaled if it had to be)
       mbar_init(&p_full[t * 2 + 1], 4);
       mbar_init(&o_full[t], 1);
       mbar_init(&o_ready[t], 4);         // the four correction warps have staged the output tile
       mbar_init(&sc_full[t], 4);
-      mbar_init(&sc_empty[t], 4);
       mbar_init(&turn[t], 1);
     }
     *abort_flag = 0;
@@ -194,48 +193,68 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
     // true maximum has grown by more than 2^kRescaleLog2 (lazy rescaling), so most KV
     // tiles need no correction of O; l is the row sum relative to that same m.
     float m = -INFINITY, l = 0.f;
+    const uint32_t tO = tmem_base + lane_off + (t == 0 ? Cfg::kTmemO0 : Cfg::kTmemO1);
     for (int j = 0; j < nblk; ++j) {
       B200FA_WAIT(&s_full[t], j & 1, 0x100 + t);
       tc_fence_after();
       uint32_t s[128];
-      tmem_ld32(tS + 0, s + 0);
-      tmem_ld32(tS + 32, s + 32);
-      tmem_ld32(tS + 64, s + 64);
-      tmem_ld32(tS + 96, s + 96);
-      tmem_wait_ld();
       float* sf = reinterpret_cast<float*>(s);
       const int col0 = j * kBN;
       // mask: causal diagonal tile and/or columns beyond Sk
       const bool need_mask = (kCausal && (col0 + kBN - 1 > row0 + t * kBM + p.causal_off)) || (col0 + kBN > p.Sk);
-      if (need_mask) {
-        const int limit = kCausal ? min(q_row + p.causal_off, p.Sk - 1) : (p.Sk - 1);  // last visible column
+      auto load_scores = [&]() {
+        tmem_ld32(tS + 0, s + 0);
+        tmem_ld32(tS + 32, s + 32);
+        tmem_ld32(tS + 64, s + 64);
+        tmem_ld32(tS + 96, s + 96);
+        tmem_wait_ld();
+        if (need_mask) {
+          const int limit = kCausal ? min(q_row + p.causal_off, p.Sk - 1) : (p.Sk - 1);  // last visible column
 #pragma unroll
-        for (int i = 0; i < 128; ++i) {
-          if (col0 + i > limit) sf[i] = -INFINITY;
+          for (int i = 0; i < 128; ++i) {
+            if (col0 + i > limit) sf[i] = -INFINITY;
+          }
         }
-      }
-      // row max, four independent chains
-      float mx0 = sf[0], mx1 = sf[1], mx2 = sf[2], mx3 = sf[3];
+      };
+      load_scores();
+      // row max, eight independent chains
+      float mx[8];
 #pragma unroll
-      for (int i = 4; i < 128; i += 4) {
-        mx0 = fmaxf(mx0, sf[i]);
-        mx1 = fmaxf(mx1, sf[i + 1]);
-        mx2 = fmaxf(mx2, sf[i + 2]);
-        mx3 = fmaxf(mx3, sf[i + 3]);
+      for (int i = 0; i < 8; ++i) mx[i] = sf[i];
+#pragma unroll
+      for (int i = 8; i < 128; i += 8) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) mx[u] = fmaxf(mx[u], sf[i + u]);
       }
-      float m_new = fmaxf(fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)), m);
+      float m_new = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+      m_new = fmaxf(m_new, m);
       // rows past the end of the sequence (or fully masked) must not produce NaN
       if (m_new == -INFINITY) m_new = 0.f;
+      // Lazy rescaling: m only moves when the true maximum has grown by more than 2^kRescaleLog2.
+      // When it does (the first tiles of a row; almost never later), O and l are rescaled, and it
+      // is this warp that rescales its 32 rows of O in tensor memory: P V of the previous tile has
+      // completed (the commit behind s_full covers it) and P V of this tile cannot start before
+      // this warp announces P.  The common step has no hand-over to another warp at all.
+      const bool moved = (m_new - m) * c > kRescaleLog2;   // always true on the first tile (m = -inf)
       float sc = 1.f;
-      if ((m_new - m) * c > kRescaleLog2) {  // always true on the first tile (m = -inf)
+      if (moved) {
         sc = ex2_approx((m - m_new) * c);
         m = m_new;
       }
-      if (j > 0) {
-        B200FA_WAIT(&sc_empty[t], (j - 1) & 1, 0x110 + t);
+      if (j > 0 && __any_sync(0xffffffffu, moved)) {
+#pragma unroll
+        for (int cidx = 0; cidx < kD / 32; ++cidx) {
+          uint32_t* o = s + (cidx & 1) * 32;   // the score registers are free here: S is read again below
+          tmem_ld32(tO + cidx * 32, o);
+          tmem_wait_ld();
+          float* of = reinterpret_cast<float*>(o);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) of[i] *= sc;
+          tmem_st32(tO + cidx * 32, o);
+        }
+        tmem_wait_st();
+        load_scores();
       }
-      sMsg[t * 128 + row] = sc;
-      mbar_arrive_warp(&sc_full[t]);
       const float mc = m * c;
       const float2 c2 = make_float2(c, c);
       const float2 nmc2 = make_float2(-mc, -mc);
@@ -268,13 +287,13 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
       l = l * sc + ((rsa.x + rsa.y) + (rsb.x + rsb.y));
     }
     if (nblk > 0) {
-      B200FA_WAIT(&sc_empty[t], (nblk - 1) & 1, 0x120 + t);
+      // the row statistics go to the epilogue warps
       sMsg[t * 128 + row] = l;
       sMax[t * 128 + row] = m;
       mbar_arrive_warp(&sc_full[t]);
     }
   } else if (warp < 12) {
-    // =========================== correction warps ===========================
+    // =========================== epilogue warps ===========================
     reg_dealloc<88>();
     const int row = threadIdx.x & 127;
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
@@ -283,7 +302,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
     auto epilogue = [&](int t) -> bool {
       const int nblk = n_t[t];
       if (nblk == 0) return true;
-      if (!mbar_wait(&sc_full[t], nblk & 1, abort_flag, p.status, 0x200 + t, p.wait_budget)) return false;
+      if (!mbar_wait(&sc_full[t], 0, abort_flag, p.status, 0x200 + t, p.wait_budget)) return false;
       const float l = sMsg[t * 128 + row];
       const float m = sMax[t * 128 + row];
       if (!mbar_wait(&o_full[t], 0, abort_flag, p.status, 0x210 + t, p.wait_budget)) return false;
@@ -331,44 +350,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
       }
       return true;
     };
-    for (int j = 0; j < n_max; ++j) {
-#pragma unroll
-      for (int t = 0; t < 2; ++t) {
-        if (j < n_t[t]) {
-          B200FA_WAIT(&sc_full[t], j & 1, 0x220 + t);
-          const float sc = sMsg[t * 128 + row];
-          mbar_arrive_warp(&sc_empty[t]);
-          if (j > 0) {
-            // Q K^T of tile j was issued after P V of tile j-1, so its commit covers both
-            B200FA_WAIT(&s_full[t], j & 1, 0x230 + t);
-            tc_fence_after();
-            if (__any_sync(0xffffffffu, sc != 1.f)) {
-              const uint32_t tO = tmem_base + lane_off + (t == 0 ? Cfg::kTmemO0 : Cfg::kTmemO1);
-#pragma unroll
-              for (int cidx = 0; cidx < kD / 32; ++cidx) {
-                uint32_t o[32];
-                tmem_ld32(tO + cidx * 32, o);
-                tmem_wait_ld();
-                float* of = reinterpret_cast<float*>(o);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) of[i] *= sc;
-                tmem_st32(tO + cidx * 32, o);
-              }
-              tmem_wait_st();
-            }
-            tc_fence_before();
-          }
-          mbar_arrive_warp(&p_full[t * 2]);
-        }
-      }
-      // a tile that just saw its last KV block can be finished while the other still runs
-      if (n_t[0] != n_t[1] && j == n_t[0] - 1) {
-        if (!epilogue(0)) goto teardown;
-      }
-    }
-    if (n_t[0] == n_t[1] || n_t[0] == 0) {
-      if (!epilogue(0)) goto teardown;
-    }
+    // (a tile that sees its last KV block a step before the other is written out while the other still runs)
+    if (!epilogue(0)) goto teardown;
     if (!epilogue(1)) goto teardown;
   } else {
     reg_dealloc<72>();

@@ -4,7 +4,8 @@
 // Math (same as the reference's backward kernels,
 // torch_mojo_backend/eager_flash_attention/fa4_bwd_kernel.mojo:1-44, 810-980, 1443-1444,
 // 1634-1662, 1855), with c = scale*log2(e):
-//   dpsum = rowsum(dO * O),  lse2 = lse*log2(e)              (preprocess)
+//   dpsum = rowsum(dO * O),  lse2 = lse*log2(e)              (preprocess; stored negated, so that
+//                                                             both enter packed two-wide adds and FMAs)
 //   P  = exp2(S*c - lse2),   dS = P * (dP - dpsum)
 //   dV = P^T dO,   dK = scale * dS^T Q,   dQ = scale * dS K
 //
@@ -55,6 +56,9 @@ struct BwdCfg {
 
 #define B200FA_WAIT(bar, parity, site) \
   if (!mbar_wait((bar), (parity), abort_flag, p.status, (site), p.wait_budget)) goto teardown
+
+// two exponentials on the special function unit
+__device__ __forceinline__ float2 exp2_mufu2(float2 x) { return make_float2(ex2_approx(x.x), ex2_approx(x.y)); }
 
 // ------------------------------------------------------------------------------------------
 // dK / dV kernel.  One CTA = one 128-row K/V tile of one (batch, kv head); it walks every
@@ -130,7 +134,32 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     if (threadIdx.x == 0 && p.status) atomicCAS(p.status, kStatusOk, 0x414c0000u);
     return;
   }
-  if (threadIdx.x == 0) {
+  // Lane 0 of the producer warp sets up the barriers and at once issues the loads the first MMAs
+  // wait for, so that their latency overlaps the TMEM allocation and the block-wide synchronisation.
+  auto load_tile = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int srow, int head) {
+#pragma unroll
+    for (int cs = 0; cs < Cfg::kSub; ++cs) tma_load_4d(dst + cs * kSubTileBytes, map, bar, cs * 64, srow, head, b);
+  };
+  // Q (with lse2) and dO (with dpsum) of step i into ring stage i % kStages
+  auto load_step = [&](int i) {
+    const int stage = i % Cfg::kStages;
+    const int h = hk * group + i / per_head;
+    const int m_tile = m_start + i % per_head;
+    const int64_t stat_off = (static_cast<int64_t>(b) * p.Hq + h) * p.Spad + m_tile * kTile;
+    float* st = sStat + stage * 256;
+    uint8_t* q_dst = sQ + stage * 2 * Cfg::kTileBytes;
+    mbar_arrive_expect_tx(&q_full[stage], Cfg::kTileBytes + 512);
+    load_tile(&mapQ, q_dst, &q_full[stage], m_tile * kTile, h);
+    bulk_load_1d(st, p.lse_log2 + stat_off, 512, &q_full[stage]);
+    mbar_arrive_expect_tx(&do_full[stage], Cfg::kTileBytes + 512);
+    load_tile(&mapDO, q_dst + Cfg::kTileBytes, &do_full[stage], m_tile * kTile, h);
+    bulk_load_1d(st + 128, p.dpsum + stat_off, 512, &do_full[stage]);
+  };
+  if (warp == 19 && lane == 0) {
+    tma_prefetch_desc(&mapK);
+    tma_prefetch_desc(&mapQ);
+    tma_prefetch_desc(&mapDO);
+    tma_prefetch_desc(&mapV);
     mbar_init(kv_full, 1);
     for (int i = 0; i < Cfg::kStages; ++i) {
       mbar_init(&q_full[i], 1);
@@ -151,16 +180,14 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     *abort_flag = 0;
     fence_mbar_init();
     fence_proxy_async_smem();
+    mbar_arrive_expect_tx(kv_full, 2 * Cfg::kTileBytes);
+    load_tile(&mapK, sK, kv_full, n0, hk);
+    if (steps > 0) load_step(0);
+    load_tile(&mapV, sV, kv_full, n0, hk);
   }
   if (warp == 16) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
-  }
-  if (warp == 19 && lane == 0) {
-    tma_prefetch_desc(&mapQ);
-    tma_prefetch_desc(&mapK);
-    tma_prefetch_desc(&mapV);
-    tma_prefetch_desc(&mapDO);
   }
   tc_fence_before();
   __syncthreads();
@@ -199,13 +226,15 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         tc_fence_before();
         mbar_arrive_warp(s_free);
       }
+      const float2 c2 = make_float2(c, c);
 #pragma unroll
       for (int e4 = 0; e4 < 8; ++e4) {
-        const float4 l4 = lse2[e4];
-        pf[e4 * 4 + 0] = ex2_approx(fmaf(pf[e4 * 4 + 0], c, -l4.x));
-        pf[e4 * 4 + 1] = ex2_approx(fmaf(pf[e4 * 4 + 1], c, -l4.y));
-        pf[e4 * 4 + 2] = ex2_approx(fmaf(pf[e4 * 4 + 2], c, -l4.z));
-        pf[e4 * 4 + 3] = ex2_approx(fmaf(pf[e4 * 4 + 3], c, -l4.w));
+        const float4 l4 = lse2[e4];   // minus lse2
+        float2 x0 = __ffma2_rn(make_float2(pf[e4 * 4 + 0], pf[e4 * 4 + 1]), c2, make_float2(l4.x, l4.y));
+        float2 x1 = __ffma2_rn(make_float2(pf[e4 * 4 + 2], pf[e4 * 4 + 3]), c2, make_float2(l4.z, l4.w));
+        x0 = exp2_mufu2(x0);
+        x1 = exp2_mufu2(x1);
+        pf[e4 * 4 + 0] = x0.x; pf[e4 * 4 + 1] = x0.y; pf[e4 * 4 + 2] = x1.x; pf[e4 * 4 + 3] = x1.y;
       }
       if (kCausal && n0 + kTile - 1 > m_tile * kTile + p.causal_off) {
         // a tile the diagonal crosses: query column q sees key row j only if j <= q + causal_off
@@ -272,12 +301,11 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
             g2 = (kb & 4u) ? g2 * p.drop.inv_keep : 0.f;
             g3 = (kb & 8u) ? g3 * p.drop.inv_keep : 0.f;
           }
-          const float a0 = pf[e4 * 4 + 0] * (g0 - d4.x);
-          const float a1 = pf[e4 * 4 + 1] * (g1 - d4.y);
-          const float a2 = pf[e4 * 4 + 2] * (g2 - d4.z);
-          const float a3 = pf[e4 * 4 + 3] * (g3 - d4.w);
-          pk[e4 * 2] = pack2<kBf16>(a0, a1);
-          pk[e4 * 2 + 1] = pack2<kBf16>(a2, a3);
+          // d4 holds minus dpsum
+          const float2 s0 = __fmul2_rn(make_float2(pf[e4 * 4 + 0], pf[e4 * 4 + 1]), __fadd2_rn(make_float2(g0, g1), make_float2(d4.x, d4.y)));
+          const float2 s1 = __fmul2_rn(make_float2(pf[e4 * 4 + 2], pf[e4 * 4 + 3]), __fadd2_rn(make_float2(g2, g3), make_float2(d4.z, d4.w)));
+          pk[e4 * 2] = pack2<kBf16>(s0.x, s0.y);
+          pk[e4 * 2 + 1] = pack2<kBf16>(s1.x, s1.y);
         }
         tmem_st16(tDP, pk);
       }
@@ -436,30 +464,12 @@ bwd_dkdv_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   } else if (warp == 19) {
     // =========================== TMA producer ===========================
     if (lane == 0) {
-      auto load_tile = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int srow, int head) {
-#pragma unroll
-        for (int cs = 0; cs < Cfg::kSub; ++cs) tma_load_4d(dst + cs * kSubTileBytes, map, bar, cs * 64, srow, head, b);
-      };
-      mbar_arrive_expect_tx(kv_full, 2 * Cfg::kTileBytes);
-      load_tile(&mapK, sK, kv_full, n0, hk);
-      load_tile(&mapV, sV, kv_full, n0, hk);
-      for (int i = 0; i < steps; ++i) {
-        const int stage = i % Cfg::kStages;
-        const int g = i / per_head;
-        const int m_tile = m_start + i % per_head;
-        const int h = hk * group + g;
+      // step 0 went out before the block-wide synchronisation
+      for (int i = 1; i < steps; ++i) {
         if (i >= Cfg::kStages) {
-          B200FA_WAIT(&qdo_empty[stage], ((i / Cfg::kStages) - 1) & 1, 0x800);
+          B200FA_WAIT(&qdo_empty[i % Cfg::kStages], ((i / Cfg::kStages) - 1) & 1, 0x800);
         }
-        const int64_t stat_off = (static_cast<int64_t>(b) * p.Hq + h) * p.Spad + m_tile * kTile;
-        float* st = sStat + stage * 256;
-        uint8_t* q_dst = sQ + stage * 2 * Cfg::kTileBytes;
-        mbar_arrive_expect_tx(&q_full[stage], Cfg::kTileBytes + 512);
-        load_tile(&mapQ, q_dst, &q_full[stage], m_tile * kTile, h);
-        bulk_load_1d(st, p.lse_log2 + stat_off, 512, &q_full[stage]);
-        mbar_arrive_expect_tx(&do_full[stage], Cfg::kTileBytes + 512);
-        load_tile(&mapDO, q_dst + Cfg::kTileBytes, &do_full[stage], m_tile * kTile, h);
-        bulk_load_1d(st + 128, p.dpsum + stat_off, 512, &do_full[stage]);
+        load_step(i);
       }
     }
   }
@@ -496,8 +506,9 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
   uint8_t* sK = smem + Cfg::kOffStream;                       // [3] tiles
   uint8_t* sV = sK + 3 * Cfg::kTileBytes;                     // [2] tiles
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kOffDqBars);
-  uint64_t* qdo_full = bars;                       // [1]
-  uint64_t* k_full = qdo_full + 1;                 // [3]
+  uint64_t* q_full = bars;                         // [1]  Q tile
+  uint64_t* do_full = q_full + 1;                  // [1]  dO tile
+  uint64_t* k_full = do_full + 1;                  // [3]
   uint64_t* k_empty = k_full + 3;                  // [3]
   uint64_t* v_full = k_empty + 3;                  // [2]
   uint64_t* v_empty = v_full + 2;                  // [2]
@@ -531,8 +542,21 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
     if (threadIdx.x == 0 && p.status) atomicCAS(p.status, kStatusOk, 0x414c0001u);
     return;
   }
-  if (threadIdx.x == 0) {
-    mbar_init(qdo_full, 1);
+  // Lane 0 of the producer warp sets up the barriers and at once issues the loads the first MMAs
+  // wait for (Q and K_0 for S_0 first), so that their latency overlaps the TMEM allocation and the
+  // block-wide synchronisation.
+  auto load_tile = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int srow, int head) {
+    mbar_arrive_expect_tx(bar, Cfg::kTileBytes);
+#pragma unroll
+    for (int cs = 0; cs < Cfg::kSub; ++cs) tma_load_4d(dst + cs * kSubTileBytes, map, bar, cs * 64, srow, head, b);
+  };
+  if (warp == 10 && lane == 0) {
+    tma_prefetch_desc(&mapQ);
+    tma_prefetch_desc(&mapK);
+    tma_prefetch_desc(&mapDO);
+    tma_prefetch_desc(&mapV);
+    mbar_init(q_full, 1);
+    mbar_init(do_full, 1);
     for (int i = 0; i < 3; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&k_empty[i], 1);
@@ -550,16 +574,16 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
     *abort_flag = 0;
     fence_mbar_init();
     fence_proxy_async_smem();
+    if (n_tiles > 0) {
+      load_tile(&mapQ, sQ, q_full, m0, h);
+      load_tile(&mapK, sK, &k_full[0], 0, hk);
+      load_tile(&mapDO, sDO, do_full, m0, h);
+      load_tile(&mapV, sV, &v_full[0], 0, hk);
+    }
   }
   if (warp == 8) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
-  }
-  if (warp == 10 && lane == 0) {
-    tma_prefetch_desc(&mapQ);
-    tma_prefetch_desc(&mapK);
-    tma_prefetch_desc(&mapV);
-    tma_prefetch_desc(&mapDO);
   }
   tc_fence_before();
   __syncthreads();
@@ -574,8 +598,9 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
     const uint32_t tDP = tmem_base + lane_off + kTmemDP + wg * 64;
     const float c = p.scale_log2;
     const int64_t stat = (static_cast<int64_t>(b) * p.Hq + h) * p.Spad + m0 + r;  // padded rows exist
-    const float lse2 = p.lse_log2[stat];
-    const float dps = p.dpsum[stat];
+    const float nlse2 = p.lse_log2[stat];   // minus lse2
+    const float ndps = p.dpsum[stat];       // minus dpsum
+    const float2 c2 = make_float2(c, c), nl2 = make_float2(nlse2, nlse2), nd2 = make_float2(ndps, ndps);
     for (int j = 0; j < n_tiles; ++j) {
       const int buf = j & 1;
       const uint32_t tS = tmem_base + lane_off + kTmemS + buf * 128 + wg * 64;
@@ -589,7 +614,12 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
         tmem_wait_ld();
         const float* sf = reinterpret_cast<const float*>(s);
 #pragma unroll
-        for (int e = 0; e < 32; ++e) pf[ch * 32 + e] = ex2_approx(fmaf(sf[e], c, -lse2));
+        for (int e = 0; e < 16; ++e) {
+          float2 x = __ffma2_rn(make_float2(sf[2 * e], sf[2 * e + 1]), c2, nl2);
+          x = exp2_mufu2(x);
+          pf[ch * 32 + 2 * e] = x.x;
+          pf[ch * 32 + 2 * e + 1] = x.y;
+        }
         if (kCausal && j * kTile + kTile - 1 > m0 + p.causal_off) {
           // a tile the diagonal crosses: query row r sees a key column only if column <= r + causal_off
           const int last_e = m0 + r + p.causal_off - (j * kTile + wg * 64 + ch * 32);   // last visible of these 32
@@ -626,9 +656,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
             g0 = (kb & 1u) ? g0 * p.drop.inv_keep : 0.f;
             g1 = (kb & 2u) ? g1 * p.drop.inv_keep : 0.f;
           }
-          const float a0 = pf[ch * 32 + 2 * e] * (g0 - dps);
-          const float a1 = pf[ch * 32 + 2 * e + 1] * (g1 - dps);
-          pk[e] = pack2<kBf16>(a0, a1);
+          const float2 a = __fmul2_rn(make_float2(pf[ch * 32 + 2 * e], pf[ch * 32 + 2 * e + 1]), __fadd2_rn(make_float2(g0, g1), nd2));
+          pk[e] = pack2<kBf16>(a.x, a.y);
         }
         tmem_st16(tS + ch * 16, pk);
       }
@@ -703,7 +732,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
       if (warp == 8) {
         // prologue: S_0, S_1
         if (n_tiles > 0) {
-          B200FA_WAIT(qdo_full, 0, 0xa00);
+          B200FA_WAIT(q_full, 0, 0xa00);
           B200FA_WAIT(&k_full[0], 0, 0xa01);
           tc_fence_after();
           issue_kmajor(tmem_base + kTmemS, kQ, kK, 0);
@@ -744,7 +773,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
         umma_commit(acc_full);
       } else if (n_tiles > 0) {
         // dP_0, then dP_{j+1} whenever the compute warps have consumed dP_j
-        B200FA_WAIT(qdo_full, 0, 0xa20);
+        B200FA_WAIT(do_full, 0, 0xa20);
         B200FA_WAIT(&v_full[0], 0, 0xa03);
         tc_fence_after();
         issue_kmajor(tDP, kDO, kV, 0);
@@ -764,23 +793,13 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
   } else if (warp == 10) {
     // =========================== TMA producer ===========================
     if (lane == 0) {
-      auto load_tile = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int srow, int head) {
-#pragma unroll
-        for (int cs = 0; cs < Cfg::kSub; ++cs) tma_load_4d(dst + cs * kSubTileBytes, map, bar, cs * 64, srow, head, b);
-      };
-      if (n_tiles > 0) {
-        mbar_arrive_expect_tx(qdo_full, 2 * Cfg::kTileBytes);
-        load_tile(&mapQ, sQ, qdo_full, m0, h);
-        load_tile(&mapDO, sDO, qdo_full, m0, h);
-      }
-      int kslot = 0;
-      for (int j = 0; j < n_tiles; ++j) {
+      // K_0 and V_0 went out before the block-wide synchronisation
+      int kslot = 1;
+      for (int j = 1; j < n_tiles; ++j) {
         if (j >= 3) { B200FA_WAIT(&k_empty[kslot], static_cast<uint32_t>((j / 3 - 1) & 1), 0xb00); }
-        mbar_arrive_expect_tx(&k_full[kslot], Cfg::kTileBytes);
         load_tile(&mapK, sK + kslot * Cfg::kTileBytes, &k_full[kslot], j * kTile, hk);
         const int vslot = j & 1;
         if (j >= 2) { B200FA_WAIT(&v_empty[vslot], ((j >> 1) - 1) & 1, 0xb01); }
-        mbar_arrive_expect_tx(&v_full[vslot], Cfg::kTileBytes);
         load_tile(&mapV, sV + vslot * Cfg::kTileBytes, &v_full[vslot], j * kTile, hk);
         if (++kslot == 3) kslot = 0;
       }
@@ -800,7 +819,7 @@ teardown:
 
 // ------------------------------------------------------------------------------------------
 // preprocess: dpsum = rowsum(dO * O), lse2 = lse * log2(e), per (b, h, row), padded to a
-// multiple of 128 rows.  Rows in [S, Spad) get lse2 = +inf and dpsum = 0 so their
+// multiple of 128 rows, both stored negated.  Rows in [S, Spad) get -lse2 = -inf and dpsum = 0 so their
 // probabilities vanish.  One row per group of D/8 lanes; every lane moves 16 bytes of O and dO.
 // ------------------------------------------------------------------------------------------
 template <int kD, bool kBf16>
@@ -849,12 +868,12 @@ __global__ void __launch_bounds__(256) bwd_preprocess_kernel(const BwdParams p) 
 #pragma unroll
   for (int off = kLanesPerRow / 2; off >= 1; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
   if (li == 0) {
-    p.dpsum[row_global] = (s < p.S) ? acc : 0.f;
-    // a row that saw no key (lse = -inf) gets +inf like the padding rows: its probabilities vanish
-    float l2 = INFINITY;
+    p.dpsum[row_global] = (s < p.S) ? -acc : 0.f;
+    // a row that saw no key (lse = -inf) gets -lse2 = -inf like the padding rows: its probabilities vanish
+    float l2 = -INFINITY;
     if (s < p.S) {
       const float l = p.lse[(static_cast<int64_t>(b) * p.Hq + h) * p.S + s];
-      if (l != -INFINITY) l2 = l * 1.4426950408889634f;
+      if (l != -INFINITY) l2 = l * -1.4426950408889634f;
     }
     p.lse_log2[row_global] = l2;
   }

@@ -39,8 +39,8 @@ struct FwdParams {
 struct BwdParams {
   View4 q, k, v, out, dout, dq, dk, dv;
   const float* lse;  // (B, Hq, S) fp32 contiguous (natural log)
-  float* dpsum;      // workspace: (B, Hq, Spad) rowsum(dO * O)
-  float* lse_log2;   // workspace: (B, Hq, Spad) lse * log2(e)
+  float* dpsum;      // workspace: (B, Hq, Spad) rowsum(dO * O)   (the tensor-core route stores both
+  float* lse_log2;   // workspace: (B, Hq, Spad) lse * log2(e)     statistics negated, the SIMT route as is)
   int B, Hq, Hkv, S, Sk, Spad, D;   // S: query rows (Spad: padded to 128); Sk: key rows
   int causal;
   int causal_off;

@@ -327,7 +327,7 @@ def run_ours(args):
                                                  lse=bufs["lse"], status=status), reps)
     bwd_part_ms = {}
     if do_bwd:
-        for name, part in (("dkdv", 2), ("dq", 4)):
+        for name, part in (("all", 7), ("dkdv", 2), ("dq", 4)):
             bwd_part_ms[name] = time_launches(
                 lambda: raw.flash_bwd(dout, q, k, v, bufs["out"], bufs["lse"], causal=cfg.causal, scale=cfg.scale,
                                       dq=bufs["dq"], dk=bufs["dk"], dv=bufs["dv"], workspace=bufs["ws"], status=status,
@@ -371,7 +371,9 @@ def run_ours(args):
         "fwd_frac_of_nominal_2250": round(cfg.fwd_flops() / (fwd_ms * 1e-3) / 1e12 / NOMINAL_BF16_TFLOPS, 4),
     }
     if do_bwd:
-        bwd_ms = ms_per_step - fwd_ms
+        # the backward timed on its own like the forward (preprocess + both kernels, as one call issues them);
+        # forward-only + backward-only need not add up to the step exactly: the step alternates the two
+        bwd_ms = bwd_part_ms["all"]
         detail.update({
             "bwd_ms": round(bwd_ms, 4), "bwd_tflops": round(cfg.bwd_flops() / (bwd_ms * 1e-3) / 1e12, 2),
             "bwd_frac_of_nominal_2250": round(cfg.bwd_flops() / (bwd_ms * 1e-3) / 1e12 / NOMINAL_BF16_TFLOPS, 4),

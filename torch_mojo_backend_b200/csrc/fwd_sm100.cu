@@ -14,11 +14,15 @@
 //               softmax warps rescale O themselves on the rare tile where a row max moved, so no
 //               KV step hands anything to these warps)
 //   warps 12-13 MMA issuers, one per query tile (one elected lane each issues tcgen05.mma / commit)
+//               per half-block: P V of one half of the key columns, then the next block's Q K^T for
+//               that half, into the S columns the P V just freed
 //   warp  14    TMA producer (Q once, then a ring of K/V tiles)
 //   warp  15    idle (it only donates registers)
 //
-// TMEM columns: S0 | S1 | O0 | O1.  P (16-bit, two per column) overwrites the first half of
-// its own S columns and is consumed as the TMEM A-operand of the P V MMA.
+// TMEM columns: S0 | S1 | O0 | O1.  The 128 key columns of a block are handled as two halves of
+// 64 with their own S columns: P of a half (16-bit, two per column) overwrites the first 32 of
+// that half's S columns and is consumed as the TMEM A-operand of the P V MMA, and the softmax of
+// one half runs while the tensor pipe works on the other.
 #include <mutex>
 
 #include "common.cuh"
@@ -34,15 +38,18 @@ constexpr int kThreads = 512;
 constexpr int kSubTileBytes = 128 * 128;  // one 128-row x 64-column (128 B) swizzled box
 
 // Lazy rescaling threshold (log2 domain): O and l are only rescaled when the running row
-// maximum grows by more than this, so P can be as large as 2^8 against a stale maximum.
-constexpr float kRescaleLog2 = 8.f;
+// maximum grows by more than this, so P can be as large as 2^12 against a stale maximum (well
+// inside fp16; what such a stale maximum costs is the weight of terms 2^-12 and less of the
+// largest, far below a 16-bit rounding step).  A rescale stalls the warp on the tile's P V
+// and rewrites its rows of O, so it should stay an event of the first blocks of a row.
+constexpr float kRescaleLog2 = 12.f;
 template <int kD>
 struct FwdCfg {
   static constexpr int kTileBytes = kBM * kD * 2;
   static constexpr int kSub = kD / 64;                  // 64-column boxes per tile
   static constexpr int kStages = (kD == 128) ? 4 : 8;   // K/V ring slots
   static constexpr int kTmemS0 = 0, kTmemS1 = 128, kTmemO0 = 256, kTmemO1 = 256 + kD;
-  static constexpr int kNumBars = 2 + 2 * kStages + 16;
+  static constexpr int kNumBars = 2 + 2 * kStages + 24;
   static constexpr int kSmemBytes = 1024 /*align slack*/ + 2 * kTileBytes + kStages * kTileBytes +
                                     4 * 128 * 4 /*msg+max*/ + kNumBars * 8 + 64;
 };
@@ -69,13 +76,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
   uint64_t* q_full = bars;                      // [2]
   uint64_t* kv_full = q_full + 2;               // [kStages]
   uint64_t* kv_empty = kv_full + Cfg::kStages;  // [kStages]
-  uint64_t* s_full = kv_empty + Cfg::kStages;   // [2]
-  uint64_t* p_full = s_full + 2;                // [2 tiles][2 halves of the KV columns]
-  uint64_t* o_full = p_full + 4;                // [2]
+  uint64_t* s_full = kv_empty + Cfg::kStages;   // [2 tiles][2 halves of the KV columns]
+  uint64_t* p_full = s_full + 4;                // [2 tiles][2 halves of the KV columns]
+  uint64_t* pv_done = p_full + 4;               // [2] one completion per P V half-block of the tile
+  uint64_t* o_full = pv_done + 2;               // [2]
   uint64_t* o_ready = o_full + 2;               // [2]
   uint64_t* sc_full = o_ready + 2;              // [2] final row statistics (l, m) of a tile are in shared memory
-  uint64_t* turn = sc_full + 2;                 // [2] MMA issuers' turn-taking
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(turn + 2);
+  uint64_t* xturn = sc_full + 2;                // [2 tiles][4 warps] the two tiles' exponential phases take turns
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xturn + 8);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5;
@@ -153,14 +161,16 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
       mbar_init(&kv_empty[i], 2);  // released by both query tiles' MMA issuers
     }
     for (int t = 0; t < 2; ++t) {
-      mbar_init(&s_full[t], 1);
+      mbar_init(&s_full[t * 2], 1);
+      mbar_init(&s_full[t * 2 + 1], 1);
+      mbar_init(&pv_done[t], 1);
       // fed by four warps each, one elected arrival per warp
       mbar_init(&p_full[t * 2], 4);      // the 4 softmax warps of the tile (P half 0 written, O rescaled if it had to be)
       mbar_init(&p_full[t * 2 + 1], 4);
       mbar_init(&o_full[t], 1);
       mbar_init(&o_ready[t], 4);         // the four correction warps have staged the output tile
       mbar_init(&sc_full[t], 4);
-      mbar_init(&turn[t], 1);
+      for (int w = 0; w < 4; ++w) mbar_init(&xturn[t * 4 + w], 1);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -194,97 +204,116 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
     // tiles need no correction of O; l is the row sum relative to that same m.
     float m = -INFINITY, l = 0.f;
     const uint32_t tO = tmem_base + lane_off + (t == 0 ? Cfg::kTmemO0 : Cfg::kTmemO1);
+    const float2 c2 = make_float2(c, c);
     for (int j = 0; j < nblk; ++j) {
-      B200FA_WAIT(&s_full[t], j & 1, 0x100 + t);
-      tc_fence_after();
-      uint32_t s[128];
-      float* sf = reinterpret_cast<float*>(s);
-      const int col0 = j * kBN;
-      // mask: causal diagonal tile and/or columns beyond Sk
-      const bool need_mask = (kCausal && (col0 + kBN - 1 > row0 + t * kBM + p.causal_off)) || (col0 + kBN > p.Sk);
-      auto load_scores = [&]() {
-        tmem_ld32(tS + 0, s + 0);
-        tmem_ld32(tS + 32, s + 32);
-        tmem_ld32(tS + 64, s + 64);
-        tmem_ld32(tS + 96, s + 96);
-        tmem_wait_ld();
-        if (need_mask) {
-          const int limit = kCausal ? min(q_row + p.causal_off, p.Sk - 1) : (p.Sk - 1);  // last visible column
-#pragma unroll
-          for (int i = 0; i < 128; ++i) {
-            if (col0 + i > limit) sf[i] = -INFINITY;
-          }
-        }
-      };
-      load_scores();
-      // row max, eight independent chains
-      float mx[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) mx[i] = sf[i];
-#pragma unroll
-      for (int i = 8; i < 128; i += 8) {
-#pragma unroll
-        for (int u = 0; u < 8; ++u) mx[u] = fmaxf(mx[u], sf[i + u]);
-      }
-      float m_new = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
-      m_new = fmaxf(m_new, m);
-      // rows past the end of the sequence (or fully masked) must not produce NaN
-      if (m_new == -INFINITY) m_new = 0.f;
-      // Lazy rescaling: m only moves when the true maximum has grown by more than 2^kRescaleLog2.
-      // When it does (the first tiles of a row; almost never later), O and l are rescaled, and it
-      // is this warp that rescales its 32 rows of O in tensor memory: P V of the previous tile has
-      // completed (the commit behind s_full covers it) and P V of this tile cannot start before
-      // this warp announces P.  The common step has no hand-over to another warp at all.
-      const bool moved = (m_new - m) * c > kRescaleLog2;   // always true on the first tile (m = -inf)
-      float sc = 1.f;
-      if (moved) {
-        sc = ex2_approx((m - m_new) * c);
-        m = m_new;
-      }
-      if (j > 0 && __any_sync(0xffffffffu, moved)) {
-#pragma unroll
-        for (int cidx = 0; cidx < kD / 32; ++cidx) {
-          uint32_t* o = s + (cidx & 1) * 32;   // the score registers are free here: S is read again below
-          tmem_ld32(tO + cidx * 32, o);
-          tmem_wait_ld();
-          float* of = reinterpret_cast<float*>(o);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) of[i] *= sc;
-          tmem_st32(tO + cidx * 32, o);
-        }
-        tmem_wait_st();
-        load_scores();
-      }
-      const float mc = m * c;
-      const float2 c2 = make_float2(c, c);
-      const float2 nmc2 = make_float2(-mc, -mc);
-      float2 rsa = make_float2(0.f, 0.f), rsb = make_float2(0.f, 0.f);
-      uint32_t pk[64];
-      uint32_t keep_bits[4] = {0, 0, 0, 0};   // dropout: one bit per column of this row of the tile
+      uint32_t keep_bits[4] = {0, 0, 0, 0};   // dropout: one bit per column of this row of the KV block
       if constexpr (kDropout) {
-        dropout_row_bits(p.drop, b * p.Hq + h, q_row, col0, keep_bits);
+        dropout_row_bits(p.drop, b * p.Hq + h, q_row, j * kBN, keep_bits);
       }
+      // The 128 key columns of a block are scored, exponentiated and fed to P V in two halves of
+      // 64, each with its own S columns: while this warp works on one half, the tensor pipe runs
+      // P V of the other half and then the next block's Q K^T into the columns that P V just freed.
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
+        const uint32_t tSh = tS + half * 64;
+        B200FA_WAIT(&s_full[t * 2 + half], j & 1, 0x100 + t * 2 + half);
+        tc_fence_after();
+        uint32_t s[64];
+        float* sf = reinterpret_cast<float*>(s);
+        const int col0 = j * kBN + half * 64;
+        // mask: causal diagonal and/or columns beyond Sk
+        const bool need_mask = (kCausal && (col0 + 63 > row0 + t * kBM + p.causal_off)) || (col0 + 64 > p.Sk);
+        auto load_scores = [&]() {
+          tmem_ld32(tSh + 0, s + 0);
+          tmem_ld32(tSh + 32, s + 32);
+          tmem_wait_ld();
+          if (need_mask) {
+            const int limit = kCausal ? min(q_row + p.causal_off, p.Sk - 1) : (p.Sk - 1);  // last visible column
 #pragma unroll
-        for (int i = half * 32; i < half * 32 + 32; ++i) {
+            for (int i = 0; i < 64; ++i) {
+              if (col0 + i > limit) sf[i] = -INFINITY;
+            }
+          }
+        };
+        load_scores();
+        // row max, eight independent chains
+        float mx[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) mx[i] = sf[i];
+#pragma unroll
+        for (int i = 8; i < 64; i += 8) {
+#pragma unroll
+          for (int u = 0; u < 8; ++u) mx[u] = fmaxf(mx[u], sf[i + u]);
+        }
+        float m_new = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+        m_new = fmaxf(m_new, m);
+        // rows past the end of the sequence (or fully masked) must not produce NaN
+        if (m_new == -INFINITY) m_new = 0.f;
+        // Lazy rescaling: nothing moves until some row's true maximum has grown by more than
+        // 2^kRescaleLog2 over the maximum its exponentials are taken against.  When one does (the
+        // first blocks of a row; rarely later), the warp rewrites its 32 rows of O anyway, so every
+        // row of the warp moves to its own true maximum: the next event is then a full threshold
+        // away for all of them, instead of each row tripping the warp at its own time.  It is this
+        // warp that rescales its rows of O in tensor memory, once the P V of the previous half-block
+        // has completed (P V of this half cannot start before this warp announces P).  The common
+        // step has no hand-over to another warp at all.
+        const bool any_moved = __any_sync(0xffffffffu, (m_new - m) * c > kRescaleLog2);   // always on the first half-block (m = -inf)
+        float sc = 1.f;
+        if (any_moved && m_new > m) {
+          sc = ex2_approx((m - m_new) * c);
+          m = m_new;
+        }
+        const int hb = 2 * j + half;   // half-block index
+        if (hb > 0 && any_moved) {
+          B200FA_WAIT(&pv_done[t], (hb - 1) & 1, 0x108 + t);
+          tc_fence_after();
+#pragma unroll
+          for (int cidx = 0; cidx < kD / 32; ++cidx) {
+            uint32_t* o = s + (cidx & 1) * 32;   // the score registers are free here: S is read again below
+            tmem_ld32(tO + cidx * 32, o);
+            tmem_wait_ld();
+            float* of = reinterpret_cast<float*>(o);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) of[i] *= sc;
+            tmem_st32(tO + cidx * 32, o);
+          }
+          tmem_wait_st();
+          load_scores();
+        }
+        // The special function unit of a scheduler is shared by one warp of each query tile.  The two
+        // take turns at the exponentials, so that one tile's loads, maxima and stores run under the
+        // other tile's exponentials instead of both tiles halving the unit's rate at the same time and
+        // leaving it idle together.  (Only the overlap depends on the turns, no result does.)
+        if (t == 0) {
+          if (hb > 0 && hb - 1 < 2 * n_t[1]) { B200FA_WAIT(&xturn[warp & 3], (hb - 1) & 1, 0x110); }
+        } else {
+          if (hb < 2 * n_t[0]) { B200FA_WAIT(&xturn[4 + (warp & 3)], hb & 1, 0x111); }
+        }
+        const float mc = m * c;
+        const float2 nmc2 = make_float2(-mc, -mc);
+        float2 rsa = make_float2(0.f, 0.f), rsb = make_float2(0.f, 0.f);
+        uint32_t pk[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
           const float2 x = __ffma2_rn(make_float2(sf[2 * i], sf[2 * i + 1]), c2, nmc2);
           float2 pv = make_float2(ex2_approx(x.x), ex2_approx(x.y));
           if (i & 1) rsb = __fadd2_rn(rsb, pv); else rsa = __fadd2_rn(rsa, pv);
           if constexpr (kDropout) {
             // the row sum keeps every probability; only what feeds P V is dropped
-            const uint32_t bits = keep_bits[i >> 4] >> ((2 * i) & 31);
+            const uint32_t bits = keep_bits[half * 2 + (i >> 4)] >> ((2 * i) & 31);
             if (!(bits & 1u)) pv.x = 0.f;
             if (!(bits & 2u)) pv.y = 0.f;
           }
           pk[i] = pack2<kBf16>(pv.x, pv.y);
         }
-        tmem_st32(tS + half * 32, pk + half * 32);
+        mbar_arrive_warp(&xturn[(1 - t) * 4 + (warp & 3)]);
+        // P (16-bit, two per column) goes over the first 32 of this half's own S columns
+        tmem_st32(tSh, pk);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive_warp(&p_full[t * 2 + half]);
+        l = l * sc + ((rsa.x + rsa.y) + (rsb.x + rsb.y));
       }
-      l = l * sc + ((rsa.x + rsa.y) + (rsb.x + rsb.y));
     }
     if (nblk > 0) {
       // the row statistics go to the epilogue warps
@@ -364,7 +393,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
       const int t = warp - 12;
       const int nblk = n_t[t];
       if (lane == 0 && nblk > 0) {
-        constexpr uint32_t idesc_qk = umma_idesc(kBf16, false, false, 128, 128);
+        constexpr uint32_t idesc_qk = umma_idesc(kBf16, false, false, 128, 64);   // one half of the key columns
         constexpr uint32_t idesc_pv = umma_idesc(kBf16, false, true, 128, kD);
         const uint32_t tS = tmem_base + (t == 0 ? Cfg::kTmemS0 : Cfg::kTmemS1);
         const uint32_t tO = tmem_base + (t == 0 ? Cfg::kTmemO0 : Cfg::kTmemO1);
@@ -373,45 +402,36 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
         const UmmaDesc dQ = umma_desc_split(smem_u32(sQ) + t * Cfg::kTileBytes, 16, 1024);  // K-major Q tile
         const UmmaDesc dK = umma_desc_split(smem_u32(sKV), 16, 1024);             // ring slot as K-major K
         const UmmaDesc dV = umma_desc_split(smem_u32(sKV), kSubTileBytes, 1024);  // ring slot as MN-major V
-        auto issue_qk = [&](uint32_t slot_lo) {
+        // S columns [64 half, 64 half + 64) = Q_t (key rows 64 half .. 64 half + 63 of the K tile)^T
+        auto issue_qk = [&](uint32_t slot_lo, int half) {
+          const uint32_t krows = umma_off(half * 64 * 128);
 #pragma unroll
           for (int kk = 0; kk < kD / 16; ++kk) {
             const uint32_t off = umma_off((kk >> 2) * kSubTileBytes + (kk & 3) * 32);
-            if (kk == 0) umma_ss_fast<false>(tS, dQ.lo + off, dQ.hi, dK.lo + slot_lo + off, dK.hi, idesc_qk);
-            else         umma_ss_fast<true>(tS, dQ.lo + off, dQ.hi, dK.lo + slot_lo + off, dK.hi, idesc_qk);
+            if (kk == 0) umma_ss_fast<false>(tS + half * 64, dQ.lo + off, dQ.hi, dK.lo + slot_lo + krows + off, dK.hi, idesc_qk);
+            else         umma_ss_fast<true>(tS + half * 64, dQ.lo + off, dQ.hi, dK.lo + slot_lo + krows + off, dK.hi, idesc_qk);
           }
         };
-        // half 0: KV rows 0-63 of the tile, half 1: rows 64-127 (P arrives in two halves)
+        // half 0: KV rows 0-63 of the tile, half 1: rows 64-127; P of a half sits in the first 32 of the half's S columns
         auto issue_pv = [&](uint32_t slot_lo, bool first, int half) {
 #pragma unroll
           for (int kq = 0; kq < 4; ++kq) {
             const int kk = half * 4 + kq;
             const uint32_t b_lo = dV.lo + slot_lo + umma_off(kk * 2048);
-            if (kk == 0 && first) umma_ts_fast<false>(tO, tS + kk * 8, b_lo, dV.hi, idesc_pv);
-            else                  umma_ts_fast<true>(tO, tS + kk * 8, b_lo, dV.hi, idesc_pv);
+            if (kk == 0 && first) umma_ts_fast<false>(tO, tS + half * 64 + kq * 8, b_lo, dV.hi, idesc_pv);
+            else                  umma_ts_fast<true>(tO, tS + half * 64 + kq * 8, b_lo, dV.hi, idesc_pv);
           }
         };
-        // The two issuing lanes take turns: a lane issues one block of MMAs (P V of the
-        // current KV tile, then Q K^T of the next) only while it holds the turn, and hands it
-        // over before it commits.  That keeps the two query tiles in anti-phase - one tile's
-        // MMAs run while the other tile is in softmax - instead of drifting into lockstep.
-        // turn[t] completes once per block of the OTHER lane; lane 0 opens.
-        int turn_k = 0;
-        auto take_turn = [&]() -> bool {
-          bool ok = true;
-          if (t == 1) ok = mbar_wait(&turn[1], turn_k & 1, abort_flag, p.status, 0x370, p.wait_budget);
-          else if (turn_k > 0) ok = mbar_wait(&turn[0], (turn_k - 1) & 1, abort_flag, p.status, 0x371, p.wait_budget);
-          ++turn_k;
-          return ok;
-        };
-        // block 0: S_t = Q_t K_0^T
+        // The two lanes issue independently: the softmax of a half only waits for its own half's
+        // S, so neither tile's chain runs through the other lane's MMAs.
+        // block 0: S_t = Q_t K_0^T, both halves
         B200FA_WAIT(&q_full[t], 0, 0x301 + t);
         B200FA_WAIT(&kv_full[0], 0, 0x300);
-        if (!take_turn()) goto teardown;
         tc_fence_after();
-        issue_qk(0);
-        mbar_arrive(&turn[1 - t]);
-        umma_commit(&s_full[t]);
+        issue_qk(0, 0);
+        umma_commit(&s_full[t * 2]);
+        issue_qk(0, 1);
+        umma_commit(&s_full[t * 2 + 1]);
         umma_commit(&kv_empty[0]);
         int slot = 1;         // ring slot of V_j; K_{j+1} follows in the next slot
         uint32_t phase = 0;   // parity of the ring pass V_j's slot is in
@@ -420,21 +440,21 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
           const uint32_t vphase = phase;
           if (++slot == Cfg::kStages) { slot = 0; phase ^= 1; }
           const bool has_next = (j + 1 < nblk);
-          // everything that can be waited for without holding the turn
           B200FA_WAIT(&kv_full[vslot], vphase, 0x310);
           if (has_next) { B200FA_WAIT(&kv_full[slot], phase, 0x340); }
-          B200FA_WAIT(&p_full[t * 2], j & 1, 0x320 + t);  // P half 0 written and O ready
-          if (!take_turn()) goto teardown;
-          tc_fence_after();
-          issue_pv(vslot * umma_off(Cfg::kTileBytes), j == 0, 0);
-          B200FA_WAIT(&p_full[t * 2 + 1], j & 1, 0x324 + t);
-          tc_fence_after();
-          issue_pv(vslot * umma_off(Cfg::kTileBytes), false, 1);
-          if (has_next) issue_qk(slot * umma_off(Cfg::kTileBytes));
-          mbar_arrive(&turn[1 - t]);
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            // one half-block: P V of this half, then the next block's Q K^T into the S columns it frees
+            B200FA_WAIT(&p_full[t * 2 + half], j & 1, 0x320 + t * 2 + half);
+            tc_fence_after();
+            issue_pv(vslot * umma_off(Cfg::kTileBytes), j == 0 && half == 0, half);
+            umma_commit(&pv_done[t]);
+            if (has_next) {
+              issue_qk(slot * umma_off(Cfg::kTileBytes), half);
+              umma_commit(&s_full[t * 2 + half]);
+            }
+          }
           if (has_next) {
-            // also tells the correction warps that P V of tile j has completed
-            umma_commit(&s_full[t]);
             umma_commit(&kv_empty[slot]);
           } else {
             umma_commit(&o_full[t]);
@@ -442,8 +462,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
           umma_commit(&kv_empty[vslot]);
           if (++slot == Cfg::kStages) { slot = 0; phase ^= 1; }
         }
-        // KV tiles only the other query tile visits still need this tile's release, and the
-        // other lane still needs its turns
+        // KV tiles only the other query tile visits still need this tile's release
         for (int j = nblk; j < n_max; ++j) {
           // K_j sits in the slot before V_j; slot/phase currently point at V_j
           const int kslot = (slot == 0) ? Cfg::kStages - 1 : slot - 1;
@@ -454,12 +473,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
           mbar_arrive(&kv_empty[slot]);
           if (++slot == Cfg::kStages) { slot = 0; phase ^= 1; }
           if (++slot == Cfg::kStages) { slot = 0; phase ^= 1; }
-          if (!take_turn()) goto teardown;
-          mbar_arrive(&turn[1 - t]);
         }
       } else if (lane == 0 && n_max > 0) {
-        // this query tile lies wholly past the end of the sequence: release each K/V slot
-        // as it fills and pass every turn straight back
+        // this query tile lies wholly past the end of the sequence: release each K/V slot as it fills
         int slot = 0;
         uint32_t phase = 0;
         for (int k = 0; k <= n_max; ++k) {
@@ -470,9 +486,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
             mbar_arrive(&kv_empty[slot]);
             if (++slot == Cfg::kStages) { slot = 0; phase ^= 1; }
           }
-          if (t == 1) { B200FA_WAIT(&turn[1], k & 1, 0x372); }
-          else if (k > 0) { B200FA_WAIT(&turn[0], (k - 1) & 1, 0x373); }
-          mbar_arrive(&turn[1 - t]);
         }
       }
     } else if (warp == 14) {

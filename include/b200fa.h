@@ -242,6 +242,16 @@ long long b200fa_wait_budget(void);
 int b200fa_status_to_error(uint32_t status_value);
 int b200fa_selftest_wait_timeout(uint32_t* status_word, long long budget_cycles, void* stream, int device);
 
+/*
+ * Shape of the tensor-core forward kernel: 2 = one thread block per SM with two 128-row query
+ * tiles, 1 = two thread blocks per SM with one query tile each, 0 = chosen per problem (one tile
+ * at head dimension 64, two at 128; the default; environment variable B200FA_FWD_TILES).  Both
+ * shapes compute the same values; the setter exists for tests and measurements.  No counterpart
+ * in the reference.
+ */
+void b200fa_set_fwd_tiles(int tiles);
+int b200fa_fwd_tiles(void);
+
 /* Human-readable text for a B200FA_ERR_* code (static storage). */
 const char* b200fa_strerror(int code);
 

@@ -126,6 +126,15 @@ def test_split_kv_entry_point_validates_before_launch():
     assert _lib.launch_count() == before
 
 
+def test_forward_kernel_shape_setter():
+    assert _lib.fwd_tiles() in (0, 1, 2)
+    for tiles in (1, 2, 0):
+        _lib.set_fwd_tiles(tiles)
+        assert _lib.fwd_tiles() == tiles
+    _lib.set_fwd_tiles(7)   # anything else means "chosen per problem"
+    assert _lib.fwd_tiles() == 0
+
+
 def test_wait_budget_and_status_helpers():
     default = _lib.wait_budget()
     assert default > 0

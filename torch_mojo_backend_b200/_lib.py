@@ -49,6 +49,8 @@ EXPORTED_SYMBOLS = (
     "b200fa_fwd_splitkv",
     "b200fa_set_wait_budget",
     "b200fa_wait_budget",
+    "b200fa_set_fwd_tiles",
+    "b200fa_fwd_tiles",
     "b200fa_status_to_error",
     "b200fa_selftest_wait_timeout",
     "b200fa_strerror",
@@ -135,6 +137,10 @@ def load() -> ctypes.CDLL:
     lib.b200fa_set_wait_budget.restype = None
     lib.b200fa_wait_budget.argtypes = []
     lib.b200fa_wait_budget.restype = ctypes.c_longlong
+    lib.b200fa_set_fwd_tiles.argtypes = [ctypes.c_int]
+    lib.b200fa_set_fwd_tiles.restype = None
+    lib.b200fa_fwd_tiles.argtypes = []
+    lib.b200fa_fwd_tiles.restype = ctypes.c_int
     lib.b200fa_status_to_error.argtypes = [ctypes.c_uint32]
     lib.b200fa_status_to_error.restype = ctypes.c_int
     lib.b200fa_selftest_wait_timeout.argtypes = [ctypes.c_void_p, ctypes.c_longlong, ctypes.c_void_p, ctypes.c_int]
@@ -243,6 +249,15 @@ def set_wait_budget(cycles: int) -> None:
 
 def wait_budget() -> int:
     return int(load().b200fa_wait_budget())
+
+
+def set_fwd_tiles(tiles: int) -> None:
+    """Query tiles per forward thread block: 0 = chosen per problem, 1 or 2 = forced (tests, measurements)."""
+    load().b200fa_set_fwd_tiles(int(tiles))
+
+
+def fwd_tiles() -> int:
+    return int(load().b200fa_fwd_tiles())
 
 
 def status_to_error(status_value: int) -> int:

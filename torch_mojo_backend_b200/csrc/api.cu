@@ -35,6 +35,19 @@ long long wait_budget() {
   return b;
 }
 
+// Query tiles per forward CTA: 0 = the launcher's rule, 1 or 2 = forced (B200FA_FWD_TILES, b200fa_set_fwd_tiles).
+std::atomic<int> g_fwd_tiles{-1};
+int fwd_tiles() {
+  int t = g_fwd_tiles.load();
+  if (t < 0) {
+    const char* env = std::getenv("B200FA_FWD_TILES");
+    t = env ? std::atoi(env) : 0;
+    if (t < 0 || t > 2) t = 0;
+    g_fwd_tiles.store(t);
+  }
+  return t;
+}
+
 // Text of the most recent CUDA failure seen by this thread (for b200fa_last_error_detail).
 thread_local char g_detail[256] = "";
 
@@ -240,6 +253,7 @@ int fwd_impl(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_tens
   p.scale = scale;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status_word;
+  p.tiles_per_cta = fwd_tiles();
   p.wait_budget = wait_budget();
 
   DeviceGuard guard(device);
@@ -347,6 +361,10 @@ const char* b200fa_last_error_detail(void) { return g_detail; }
 void b200fa_set_wait_budget(long long cycles) { g_wait_budget.store(cycles > 0 ? cycles : 0); }
 
 long long b200fa_wait_budget(void) { return wait_budget(); }
+
+void b200fa_set_fwd_tiles(int tiles) { g_fwd_tiles.store(tiles == 1 || tiles == 2 ? tiles : 0); }
+
+int b200fa_fwd_tiles(void) { return fwd_tiles(); }
 
 uint32_t b200fa_dropout_threshold(float p) {
   if (!(p > 0.f)) return 0;

@@ -32,6 +32,7 @@ struct FwdParams {
   float scale;       // softmax scale
   float scale_log2;  // scale * log2(e)
   uint32_t* status;  // optional device status word
+  int tiles_per_cta;      // forward kernel shape: 0 = chosen by the launcher, 1 or 2 = forced
   long long wait_budget;  // SM cycles any single internal wait may take before the kernel gives up
   DropoutParams drop;
 };

@@ -6,7 +6,9 @@
 // 1138-1160): S = Q K^T, causal mask, online softmax in the exp2 domain with
 // c = scale*log2(e), P rounded to the 16-bit input type before P V, O / rowsum and
 // LSE = rowmax*scale + ln(rowsum).  The structure is new: one CTA owns TWO 128-row query
-// tiles of one (batch, head) and ping-pongs them through the tensor core.
+// tiles of one (batch, head) and ping-pongs them through the tensor core (kTiles = 2, below);
+// at head dimension 64 two CTAs with ONE query tile each share an SM instead (kTiles = 1: warps
+// 0-3 softmax, 4-7 epilogue, 8 MMA, 10 TMA).
 //
 //   warps 0-3   softmax of query tile 0   (thread i <-> TMEM lane i <-> query row i)
 //   warps 4-7   softmax of query tile 1
@@ -34,7 +36,6 @@ namespace {
 
 constexpr int kBM = 128;        // query rows per tile
 constexpr int kBN = 128;        // key rows per tile
-constexpr int kThreads = 512;
 constexpr int kSubTileBytes = 128 * 128;  // one 128-row x 64-column (128 B) swizzled box
 
 // Lazy rescaling threshold (log2 domain): O and l are only rescaled when the running row
@@ -43,33 +44,44 @@ constexpr int kSubTileBytes = 128 * 128;  // one 128-row x 64-column (128 B) swi
 // largest, far below a 16-bit rounding step).  A rescale stalls the warp on the tile's P V
 // and rewrites its rows of O, so it should stay an event of the first blocks of a row.
 constexpr float kRescaleLog2 = 12.f;
-template <int kD>
+// kTiles = 2: one CTA per SM owns two query tiles (512 threads, the whole of TMEM and shared memory).
+// kTiles = 1: a CTA owns one query tile with half of everything (384 threads, 256 TMEM columns, half
+// the K/V ring), so that two CTAs share an SM and each one's set-up, first loads and epilogue run
+// under the other's KV loop: for problems made of many short CTAs, where that fixed cost dominates.
+template <int kD, int kTiles>
 struct FwdCfg {
   static constexpr int kTileBytes = kBM * kD * 2;
   static constexpr int kSub = kD / 64;                  // 64-column boxes per tile
-  static constexpr int kStages = (kD == 128) ? 4 : 8;   // K/V ring slots
-  static constexpr int kTmemS0 = 0, kTmemS1 = 128, kTmemO0 = 256, kTmemO1 = 256 + kD;
+  static constexpr int kStages = ((kD == 128) ? 4 : 8) / (kTiles == 2 ? 1 : 2);   // K/V ring slots
+  static constexpr int kThreads = kTiles == 2 ? 512 : 384;
+  // warp roles: 4 softmax warps per tile, 4 epilogue warps, one MMA-issuing warp per tile, one TMA warp
+  static constexpr int kEpiWarp0 = 4 * kTiles, kMmaWarp0 = kEpiWarp0 + 4, kTmaWarp = kMmaWarp0 + 2;
+  // registers per thread after the set-up (the launch gives every warp 65536 / threads per SM)
+  static constexpr int kRegSoftmax = kTiles == 2 ? 176 : 144, kRegEpi = kTiles == 2 ? 88 : 56, kRegRest = kTiles == 2 ? 72 : 40;
+  static constexpr int kTmemCols = kTiles == 2 ? 512 : 256;
+  static constexpr int kTmemS0 = 0, kTmemS1 = 128, kTmemO0 = 128 * kTiles, kTmemO1 = 128 * kTiles + kD;
   static constexpr int kNumBars = 2 + 2 * kStages + 24;
-  static constexpr int kSmemBytes = 1024 /*align slack*/ + 2 * kTileBytes + kStages * kTileBytes +
+  static constexpr int kSmemBytes = 1024 /*align slack*/ + kTiles * kTileBytes + kStages * kTileBytes +
                                     4 * 128 * 4 /*msg+max*/ + kNumBars * 8 + 64;
 };
 
 struct FwdSched {
-  int npairs;      // 256-row query pairs per (b, h)
+  int npairs;      // query units (256-row pairs, or 128-row tiles of the one-tile kernel) per (b, h)
   int group;       // heads scheduled together so their K/V stay L2-resident
   int nkv_total;   // ceil(Sk / 128)
+  bool one_tile;   // the one-tile-per-CTA kernel (two CTAs per SM)
 };
 
-template <int kD, bool kBf16, bool kCausal, bool kDropout>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int kD, bool kBf16, bool kCausal, bool kDropout, int kTiles>
+__global__ void __launch_bounds__(FwdCfg<kD, kTiles>::kThreads, kTiles == 2 ? 1 : 2)
 fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
            const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapO, const FwdParams p,
            const FwdSched sched) {
-  using Cfg = FwdCfg<kD>;
+  using Cfg = FwdCfg<kD, kTiles>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;                                   // 2 tiles
-  uint8_t* sKV = sQ + 2 * Cfg::kTileBytes;              // ring
+  uint8_t* sKV = sQ + kTiles * Cfg::kTileBytes;         // ring
   float* sMsg = reinterpret_cast<float*>(sKV + Cfg::kStages * Cfg::kTileBytes);  // [2][128]
   float* sMax = sMsg + 256;                             // [2][128]
   uint64_t* bars = reinterpret_cast<uint64_t*>(sMax + 256);
@@ -107,12 +119,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
   const int b = bh / p.Hq;
   const int h = bh - b * p.Hq;
   const int hk = h / (p.Hq / p.Hkv);
-  const int row0 = pair * 2 * kBM;  // first query row of tile 0
+  const int row0 = pair * kTiles * kBM;  // first query row of tile 0
 
   // KV tiles each query tile visits
-  int n_t[2];
+  int n_t[2] = {0, 0};
 #pragma unroll
-  for (int t = 0; t < 2; ++t) {
+  for (int t = 0; t < kTiles; ++t) {
     const int r0 = row0 + t * kBM;
     if (r0 >= p.Sq) {
       n_t[t] = 0;
@@ -146,19 +158,19 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
       // Q tile 0 rides ahead of K_0, Q tile 1 right behind it
       if (n_t[0] > 0) load_tile(&mapQ, sQ, &q_full[0], row0, h);
       load_tile(&mapK, sKV + slot * Cfg::kTileBytes, &kv_full[slot], 0, hk);
-      if (n_t[1] > 0) load_tile(&mapQ, sQ + Cfg::kTileBytes, &q_full[1], row0 + kBM, h);
+      if (kTiles == 2 && n_t[1] > 0) load_tile(&mapQ, sQ + Cfg::kTileBytes, &q_full[1], row0 + kBM, h);
     } else {
       load_tile((seq & 1) ? &mapV : &mapK, sKV + slot * Cfg::kTileBytes, &kv_full[slot], j * kBN, hk);
     }
   };
   const int n_loads = 2 * n_max;
   constexpr int kEarlyLoads = 2;   // Q, K_0 and V_0: what the first MMAs wait for; more would only delay the sync
-  if (warp == 14 && lane == 0) {
+  if (warp == Cfg::kTmaWarp && lane == 0) {
     mbar_init(&q_full[0], 1);
     mbar_init(&q_full[1], 1);
     for (int i = 0; i < Cfg::kStages; ++i) {
       mbar_init(&kv_full[i], 1);
-      mbar_init(&kv_empty[i], 2);  // released by both query tiles' MMA issuers
+      mbar_init(&kv_empty[i], kTiles);  // released by every query tile's MMA issuer
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(&s_full[t * 2], 1);
@@ -177,8 +189,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
     fence_proxy_async_smem();
     for (int seq = 0; seq < min(n_loads, kEarlyLoads); ++seq) produce(seq);
   }
-  if (warp == 12) {
-    tmem_alloc(tmem_slot, 512);
+  if (warp == Cfg::kMmaWarp0) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -189,9 +201,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
 #define B200FA_WAIT(bar, parity, site) \
   if (!mbar_wait((bar), (parity), abort_flag, p.status, (site), p.wait_budget)) goto teardown
 
-  if (warp < 8) {
+  if (warp < 4 * kTiles) {
     // =========================== softmax warps ===========================
-    reg_alloc<176>();
+    reg_alloc<Cfg::kRegSoftmax>();
     const int t = warp >> 2;
     const int row = threadIdx.x & 127;
     const int nblk = n_t[t];
@@ -284,10 +296,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
         // take turns at the exponentials, so that one tile's loads, maxima and stores run under the
         // other tile's exponentials instead of both tiles halving the unit's rate at the same time and
         // leaving it idle together.  (Only the overlap depends on the turns, no result does.)
-        if (t == 0) {
-          if (hb > 0 && hb - 1 < 2 * n_t[1]) { B200FA_WAIT(&xturn[warp & 3], (hb - 1) & 1, 0x110); }
-        } else {
-          if (hb < 2 * n_t[0]) { B200FA_WAIT(&xturn[4 + (warp & 3)], hb & 1, 0x111); }
+        if constexpr (kTiles == 2) {
+          if (t == 0) {
+            if (hb > 0 && hb - 1 < 2 * n_t[1]) { B200FA_WAIT(&xturn[warp & 3], (hb - 1) & 1, 0x110); }
+          } else {
+            if (hb < 2 * n_t[0]) { B200FA_WAIT(&xturn[4 + (warp & 3)], hb & 1, 0x111); }
+          }
         }
         const float mc = m * c;
         const float2 nmc2 = make_float2(-mc, -mc);
@@ -306,7 +320,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
           }
           pk[i] = pack2<kBf16>(pv.x, pv.y);
         }
-        mbar_arrive_warp(&xturn[(1 - t) * 4 + (warp & 3)]);
+        if constexpr (kTiles == 2) mbar_arrive_warp(&xturn[(1 - t) * 4 + (warp & 3)]);
         // P (16-bit, two per column) goes over the first 32 of this half's own S columns
         tmem_st32(tSh, pk);
         tmem_wait_st();
@@ -321,9 +335,9 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
       sMax[t * 128 + row] = m;
       mbar_arrive_warp(&sc_full[t]);
     }
-  } else if (warp < 12) {
+  } else if (warp < Cfg::kEpiWarp0 + 4) {
     // =========================== epilogue warps ===========================
-    reg_dealloc<88>();
+    reg_dealloc<Cfg::kRegEpi>();
     const int row = threadIdx.x & 127;
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const int es_shift = 1;  // 16-bit elements
@@ -369,7 +383,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
       if (q_row < p.Sq) {
         p.lse[(static_cast<int64_t>(b) * p.Hq + h) * p.Sq + q_row] = l > 0.f ? m * p.scale + logf(l) : -INFINITY;
       }
-      if (warp == 8 && lane == 0) {
+      if (warp == Cfg::kEpiWarp0 && lane == 0) {
         if (!mbar_wait(&o_ready[t], 0, abort_flag, p.status, 0x218 + t, p.wait_budget)) return false;
 #pragma unroll
         for (int cs = 0; cs < Cfg::kSub; ++cs) {
@@ -381,16 +395,18 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
     };
     // (a tile that sees its last KV block a step before the other is written out while the other still runs)
     if (!epilogue(0)) goto teardown;
-    if (!epilogue(1)) goto teardown;
+    if constexpr (kTiles == 2) {
+      if (!epilogue(1)) goto teardown;
+    }
   } else {
-    reg_dealloc<72>();
-    if (warp == 12 || warp == 13) {
+    reg_dealloc<Cfg::kRegRest>();
+    if (warp >= Cfg::kMmaWarp0 && warp < Cfg::kMmaWarp0 + kTiles) {
       // =========================== MMA issuers (one per query tile) ===========================
       // A tcgen05.mma only issues once the tensor pipe has room, so the issuing lane is stalled
       // for about as long as its MMAs run, and every wait or commit it executes in between is
       // time the pipe could drain.  Giving each query tile its own issuing lane lets one
       // lane's waits overlap the other lane's MMAs.
-      const int t = warp - 12;
+      const int t = warp - Cfg::kMmaWarp0;
       const int nblk = n_t[t];
       if (lane == 0 && nblk > 0) {
         constexpr uint32_t idesc_qk = umma_idesc(kBf16, false, false, 128, 64);   // one half of the key columns
@@ -488,7 +504,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
           }
         }
       }
-    } else if (warp == 14) {
+    } else if (warp == Cfg::kTmaWarp) {
       // =========================== TMA producer ===========================
       if (lane == 0) {
         // the first kEarlyLoads entries went out before the block-wide synchronisation
@@ -505,21 +521,21 @@ fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUt
 teardown:
 #undef B200FA_WAIT
   // the staged output tiles must have been read before shared memory is given back
-  if (warp == 8 && lane == 0) tma_store_wait_read();
+  if (warp == Cfg::kEpiWarp0 && lane == 0) tma_store_wait_read();
   tc_fence_before();
   __syncthreads();
-  if (warp == 12) {
+  if (warp == Cfg::kMmaWarp0) {
     __syncwarp();
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
   }
 }
 
-template <int kD, bool kBf16, bool kCausal, bool kDropout>
-cudaError_t launch_one(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
+template <int kD, bool kBf16, bool kCausal, bool kDropout, int kTiles>
+cudaError_t launch_tiles(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
                        const FwdParams& p, const FwdSched& sched, cudaStream_t stream) {
-  using Cfg = FwdCfg<kD>;
-  auto kern = fwd_kernel<kD, kBf16, kCausal, kDropout>;
+  using Cfg = FwdCfg<kD, kTiles>;
+  auto kern = fwd_kernel<kD, kBf16, kCausal, kDropout, kTiles>;
   // cudaFuncSetAttribute once per device for THIS kernel (the flags are statics of this function
   // template: kernels of the same signature must not share them), safe against concurrent first calls
   static std::once_flag once[64];
@@ -537,8 +553,30 @@ cudaError_t launch_one(const CUtensorMap& mq, const CUtensorMap& mk, const CUten
   }
   if (e != cudaSuccess) return e;
   const int grid = sched.npairs * p.B * p.Hq;
-  kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(mq, mk, mv, mo, p, sched);
+  kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(mq, mk, mv, mo, p, sched);
   return cudaGetLastError();
+}
+
+template <int kD, bool kBf16, bool kCausal, bool kDropout>
+cudaError_t launch_one(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const CUtensorMap& mo,
+                       const FwdParams& p, FwdSched sched, cudaStream_t stream) {
+  if (sched.one_tile) {
+    sched.npairs = (p.Sq + kBM - 1) / kBM;
+    return launch_tiles<kD, kBf16, kCausal, kDropout, 1>(mq, mk, mv, mo, p, sched, stream);
+  }
+  return launch_tiles<kD, kBf16, kCausal, kDropout, 2>(mq, mk, mv, mo, p, sched, stream);
+}
+
+// Which kernel shape.  Two CTAs per SM with one query tile each hide a CTA's set-up, first loads
+// and epilogue under the other CTA's KV loop, but have half the K/V ring each and load every K/V
+// tile once per query tile instead of once per pair.  Measured on B200: at D = 64 (16 KB tiles, the
+// ring still four deep) it is 11-13 % faster on problems of many short CTAs (B32 H12 S1024: 0.145
+// -> 0.129 ms) and equal on long ones; at D = 128 the ring of two stalls every P V on its V load
+// (C3 0.49 -> 0.65 ms).  `forced` (0 = this rule, 1, 2) is for tests and measurements.
+bool choose_one_tile(const FwdParams& p, int forced) {
+  if (forced == 1) return true;
+  if (forced == 2) return false;
+  return p.D == 64;
 }
 
 template <int kD, bool kBf16>
@@ -572,6 +610,7 @@ cudaError_t launch_fwd_sm100(const FwdParams& p, int dtype, cudaStream_t stream,
   if (group < 1) group = 1;
   if (group > total_bh) group = total_bh;
   sched.group = static_cast<int>(group);
+  sched.one_tile = choose_one_tile(p, p.tiles_per_cta);
   cudaError_t e;
   if (p.D == 128) {
     e = bf16 ? launch_mask<128, true>(mq, mk, mv, mo, p, sched, stream)

@@ -620,9 +620,16 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ 
           pf[ch * 32 + 2 * e] = x.x;
           pf[ch * 32 + 2 * e + 1] = x.y;
         }
-        if (kCausal && j * kTile + kTile - 1 > m0 + p.causal_off) {
-          // a tile the diagonal crosses: query row r sees a key column only if column <= r + causal_off
-          const int last_e = m0 + r + p.causal_off - (j * kTile + wg * 64 + ch * 32);   // last visible of these 32
+        // Columns to blank: beyond the causal diagonal, and beyond the last key.  K rows past Sk are
+        // zero-filled, so their dS would be multiplied by zero, but with a very negative lse their
+        // probability exp2(0 - lse2) overflows the 16-bit dS to inf, and inf * 0 is NaN.
+        const bool diagonal = kCausal && j * kTile + kTile - 1 > m0 + p.causal_off;
+        const bool past_end = (j + 1) * kTile > p.Sk;
+        if (diagonal || past_end) {
+          const int col0 = j * kTile + wg * 64 + ch * 32;
+          int last_e = 31;   // last visible of these 32
+          if (diagonal) last_e = m0 + r + p.causal_off - col0;   // query row r sees a key column only if column <= r + causal_off
+          if (past_end) last_e = min(last_e, p.Sk - 1 - col0);
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
             if (e > last_e) pf[ch * 32 + e] = 0.f;

@@ -159,6 +159,56 @@ def test_randomised_shapes_agree_with_the_exact_fp32_kernels():
             assert (got.float() - ref.float()).abs().max().item() < bound, f"{name}: {what}"
 
 
+def test_randomised_masks_logit_scales_dropout_and_kernel_shapes_agree_with_the_exact_fp32_kernels():
+    """The same kind of seeded sweep over what lies around the reference's gate: both causal
+    alignments over unequal lengths (rows that see no key included), logits up to six times the
+    usual spread (rescale events, very negative logsumexp), dropout, and both shapes of the forward
+    kernel; lse must be -inf exactly where the exact-fp32 kernel says so."""
+    import random
+
+    from torch_mojo_backend_b200 import _lib
+
+    rng = random.Random(20261125)
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lengths = [1, 17, 64, 127, 128, 129, 255, 256, 300, 511, 640, 1000, 1537]
+    try:
+        for _ in range(160):
+            D = rng.choice([64, 128])
+            dtype = rng.choice([torch.bfloat16, torch.float16])
+            Hkv, group, B = rng.choice([1, 2, 3]), rng.choice([1, 1, 2, 4]), rng.choice([1, 2])
+            mode = rng.choice([0, 1, 1, 2])
+            Sq = rng.choice(lengths + [rng.randint(1, 1800)])
+            Sk = rng.choice([Sq, Sq, rng.randint(1, 1800), 128, 1])
+            spread = rng.choice([0.5, 1.0, 2.0, 3.0])
+            tiles = rng.choice([0, 0, 1, 2])
+            drop = (rng.choice([0.1, 0.5]), rng.getrandbits(60), rng.randrange(0, 1 << 20, 4)) if rng.random() < 0.2 else None
+            q = (torch.randn(B, Hkv * group, Sq, D, device="cuda", generator=gen) * spread).to(dtype)
+            k = (torch.randn(B, Hkv, Sk, D, device="cuda", generator=gen) * spread).to(dtype)
+            v = (torch.randn(B, Hkv, Sk, D, device="cuda", generator=gen) * 0.5).to(dtype)
+            do = torch.randn(B, Hkv * group, Sq, D, device="cuda", generator=gen).to(dtype)
+            status.zero_()
+            _lib.set_fwd_tiles(tiles)
+            out, lse = raw.flash_fwd(q, k, v, causal=mode, status=status, dropout=drop)
+            grads = raw.flash_bwd(do, q, k, v, out, lse, causal=mode, status=status, dropout=drop)
+            s_out, s_lse = raw.flash_fwd(q, k, v, causal=mode, simt=True, dropout=drop)
+            s_grads = raw.flash_bwd(do, q, k, v, s_out, s_lse, causal=mode, simt=True, dropout=drop)
+            torch.cuda.synchronize()
+            what = f"{dtype} B{B} Hq{Hkv * group} Hkv{Hkv} Sq{Sq} Sk{Sk} D{D} mode={mode} spread={spread} tiles={tiles} drop={drop}"
+            assert int(status.item()) == 0, what
+            assert torch.equal(torch.isinf(lse), torch.isinf(s_lse)), what
+            seen = torch.isfinite(s_lse)
+            if seen.any():
+                assert (lse[seen] - s_lse[seen]).abs().max().item() < 2 * TOL_LSE, what
+            for name, got, ref in zip(("out", "dq", "dk", "dv"), (out,) + tuple(grads), (s_out,) + tuple(s_grads)):
+                assert torch.isfinite(got.float()).all().item(), f"{name}: {what}"
+                # both sides are rounded to 16 bits: allow the tolerance plus one ulp of the larger values
+                bound = TOL_16BIT + 2.0 ** -7 * ref.float().abs().max().item()
+                assert (got.float() - ref.float()).abs().max().item() < bound, f"{name}: {what}"
+    finally:
+        _lib.set_fwd_tiles(0)
+
+
 @pytest.mark.parametrize("name", golden_names())
 def test_golden_fixtures(name):
     meta, q, k, v, dout, exp = load_golden(name)

@@ -45,6 +45,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 NOMINAL_BF16_TFLOPS = 2250.0
+SEED_NOTE_WEAK = "torch.Generator().manual_seed(rank); q,k,v,dO drawn in that order"
 FALLBACK_BF16_TFLOPS = 1590.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from one
 # ncu capture of that kernel on that workload (bytes per launch)
@@ -286,7 +287,7 @@ def run_ours(args):
         cpu_full, slices = None, None
         cfg = cfg_full
         q, k, v, dout = (t.to(dev) for t in O.make_inputs(cfg, seed=rank))
-        seed_note = "torch.Generator().manual_seed(rank); q,k,v,dO drawn in that order"
+        seed_note = SEED_NOTE_WEAK
     bufs = make_bufs(_lib, raw, q, k, v, cfg)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
 
@@ -550,10 +551,13 @@ def run_reference(args):
         "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(1e3 * statistics.median(secs_all), 2), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": str(cfg.dtype).replace("torch.", ""), "data": "synthetic",
+        # the same `config` as the GPU arm prints for this workload (the CPU sample is in cpu_baseline.sample)
         "config": {"workload": f"{cfg.name}: {'causal' if cfg.causal else 'non-causal'} "
                                f"{'fwd+bwd' if cfg.backward else 'fwd'} B={cfg.B} Hq={cfg.Hq} Hkv={cfg.Hkv} S={cfg.S} "
                                f"D={cfg.D} per GPU",
-                   "cpu_sample": sample},
+                   "l2": "inputs larger than L2 (no flush needed)" if cfg.fwd_bytes() > 126e6
+                         else "working set fits in L2 (L2-hot number)",
+                   "seed": SEED_NOTE_WEAK},
         "cpu_baseline": {"value": round(value, 4), "unit": "TFLOP/s", "cores": threads, "kind": "port",
                          "sample": sample},
         "e2e": {"value": round(value, 4), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},

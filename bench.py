@@ -432,11 +432,17 @@ def run_e2e(cfg, q_dev, k_dev, v_dev, dout_dev, rank, world, local, args):
       whole batch on `mojo` tensors, every copy and kernel on one stream;
     * ``pipelined``: ``torch_mojo_backend_b200.HostAttentionPipeline`` - the batch cut into
       pieces of whole (batch entry, kv-head group) units that go through the two registered
-      flash operators with uploads, kernels and downloads on three streams.  Same inputs, same
-      bytes moved, bitwise the same results (checked here before timing).
+      flash operators with uploads, kernels and downloads on three streams, the host waiting for
+      each step's results before it enqueues the next step.  Same inputs, same bytes moved,
+      bitwise the same results (checked here before timing).
+    * ``overlapped``: the same pipeline with two steps in flight: the host enqueues step i + 1,
+      then waits for step i's results (``PendingPass.wait``; two sets of result buffers), so the
+      uploads of a step run under the downloads of the step before and neither PCIe direction idles
+      while a step fills or drains.  Every step's inputs are still uploaded and its results still
+      land in host memory and are waited for inside the timed region.
 
-    ``value`` is the pipelined number when the step is large enough to repay the pipelining
-    (more than one piece), else the single call.
+    ``value`` is the best of the pipelined ways when the step is large enough to repay the
+    pipelining (more than one piece), else the single call.
     """
     import torch_mojo_backend_b200 as tmb
 
@@ -448,7 +454,7 @@ def run_e2e(cfg, q_dev, k_dev, v_dev, dout_dev, rank, world, local, args):
         p.copy_(t.cpu())
         host.append(p)
     hq, hk, hv, hdo = host
-    steps = max(1, min(args.steps, 5))
+    steps = max(1, min(args.steps, 10))
     gqa = cfg.Hq != cfg.Hkv
     h2d = sum(t.numel() * t.element_size() for t in ((hq, hk, hv, hdo) if cfg.backward else (hq, hk, hv)))
     # results land in pre-pinned host buffers: out, and dq/dk/dv when the config has a backward
@@ -505,6 +511,41 @@ def run_e2e(cfg, q_dev, k_dev, v_dev, dout_dev, rank, world, local, args):
     same = all(torch.equal(a, b) for a, b in zip(ref, (res_out,) + (res_grads or ())))
     pipelined()
     ms_pipe = time_steps(pipelined)
+
+    # two steps in flight: a second set of result buffers, and the host always one step behind
+    res2_out = tmb.pinned_empty(hq.shape, hq.dtype)
+    res2_grads = tuple(tmb.pinned_empty(t.shape, t.dtype) for t in (hq, hk, hv)) if cfg.backward else None
+    sets = ((res_out, res_grads), (res2_out, res2_grads))
+
+    # with steps overlapping, a step needs no fine pieces of its own to fill and drain quickly: larger
+    # pieces mean fewer copies and less dispatch (measured on C3: 8.5 ms a step with 40 MB pieces, 8.2 with 96 MB)
+    pipe_over = tmb.HostAttentionPipeline(local, piece_bytes=96 << 20)
+    n_pieces_over = len(pipe_over.pieces(hq, hk, cfg.backward))
+
+    def overlapped_steps(n):
+        waiting = None
+        for i in range(n):
+            o, g = sets[i % 2]
+            p = pipe_over.enqueue(hq, hk, hv, hdo if cfg.backward else None, is_causal=cfg.causal, scale=cfg.scale, out=o,
+                             grads=g)
+            if waiting is not None:
+                waiting.wait()      # the host has step i - 1's results before it goes on to step i + 1
+            waiting = p
+        waiting.wait()
+        pipe_over.synchronize()
+
+    for t in (res_out, res2_out) + (res_grads or ()) + (res2_grads or ()):
+        t.zero_()
+    overlapped_steps(2)
+    same_over = all(torch.equal(a, b) for a, b in zip(ref, (res_out,) + (res_grads or ()))) and \
+        all(torch.equal(a, b) for a, b in zip(ref, (res2_out,) + (res2_grads or ())))
+    barrier(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    overlapped_steps(steps)     # ends with the current stream ordered behind the pipeline's streams
+    e1.record()
+    barrier(world)
+    ms_over = max_over_ranks(e0.elapsed_time(e1), world) / steps
     tf = lambda ms: round(world * flops / (ms * 1e-3) / 1e12, 2)
     gbs = lambda nbytes, ms: round(nbytes / (ms * 1e-3) / 1e9, 2)
     entry = lambda ms, api, extra: dict({"value": tf(ms), "ms_per_step": round(ms, 3), "api": api,
@@ -512,8 +553,12 @@ def run_e2e(cfg, q_dev, k_dev, v_dev, dout_dev, rank, world, local, args):
     single = entry(ms_single, "F.scaled_dot_product_attention + backward on mojo tensors, whole batch, one stream", {})
     piped = entry(ms_pipe, "torch_mojo_backend_b200.HostAttentionPipeline: the batch in pieces; uploads, kernels and "
                            "downloads on three streams", {"pieces": n_pieces, "matches_single_call_bitwise": bool(same)})
+    over = entry(ms_over, "HostAttentionPipeline.enqueue / PendingPass.wait: as pipelined, two steps in flight, the host "
+                          "one step behind", {"pieces": n_pieces_over, "matches_single_call_bitwise": bool(same_over)})
     use_pipe = n_pieces > 1 and same
     best_ms, mode = (ms_pipe, "pipelined") if use_pipe else (ms_single, "single_call")
+    if use_pipe and same_over and ms_over < ms_pipe:
+        best_ms, mode = ms_over, "overlapped" 
     try:
         cores = sorted(os.sched_getaffinity(0))
     except (AttributeError, OSError):
@@ -524,7 +569,7 @@ def run_e2e(cfg, q_dev, k_dev, v_dev, dout_dev, rank, world, local, args):
             "bound": "host link: the step moves h2d + d2h bytes over PCIe around a few ms of kernels; with several "
                      "ranks on one host the copies of all ranks share the host's memory and PCIe fabric",
             "host_cores_of_this_rank": len(cores), "ranks_on_host": world,
-            "pipelined": piped, "single_call": single}
+            "overlapped": over, "pipelined": piped, "single_call": single}
 
 
 def run_reference(args):

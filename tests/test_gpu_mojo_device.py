@@ -131,6 +131,19 @@ def test_host_attention_pipeline_is_bitwise_the_single_call(mojo_registered):
         assert torch.equal(res_out, out.detach().cpu())
         assert torch.equal(grads[0], mq.grad.cpu()) and torch.equal(grads[1], mk.grad.cpu())
         assert torch.equal(grads[2], mv.grad.cpu())
+    # two passes in flight with different inputs and their own result buffers: the second is enqueued
+    # before the first is waited for, and each lands exactly what a pass on its own lands
+    hq2 = tmb.pinned_empty(hq.shape, hq.dtype)
+    hq2.copy_(hq.flip(2))
+    first = pipe.enqueue(hq, hk, hv, hdo, is_causal=True)
+    second = pipe.enqueue(hq2, hk, hv, hdo, is_causal=True)
+    out1, grads1 = first.wait()
+    assert torch.equal(out1, out.detach().cpu()) and torch.equal(grads1[0], mq.grad.cpu())
+    out2, grads2 = second.wait()
+    alone_out, alone_grads = pipe.run(hq2, hk, hv, hdo, is_causal=True)
+    pipe.synchronize()
+    assert torch.equal(out2, alone_out) and all(torch.equal(a, b) for a, b in zip(grads2, alone_grads))
+    assert not torch.equal(out2, out1)
     # forward only, one batch entry larger than a piece: its kv-head groups are the pieces
     pipe2 = tmb.HostAttentionPipeline(0, piece_bytes=1 << 20)
     assert len(pipe2.pieces(hq, hk, False)) == 2 * B

@@ -19,9 +19,34 @@ from __future__ import annotations
 import torch
 
 
+class PendingPass:
+    """One enqueued pass of a ``HostAttentionPipeline``: its pinned host result tensors and the
+    event behind its last download.  ``wait()`` blocks the host until the results are complete
+    and gives the pass's device tensors back to the allocator."""
+
+    def __init__(self, out, grads, done, keep):
+        self.out = out
+        self.grads = grads
+        self._done = done
+        self._keep = keep
+
+    def wait(self):
+        if self._done is not None:
+            self._done.synchronize()
+            self._done = None
+            self._keep.clear()
+        return self.out, self.grads
+
+
 class HostAttentionPipeline:
     """``run`` computes ``out`` (and ``dq, dk, dv`` when ``dout`` is given) for pinned host
-    tensors shaped (B, Hq, S, D) / (B, Hkv, S, D), writing into pinned host result tensors."""
+    tensors shaped (B, Hq, S, D) / (B, Hkv, S, D), writing into pinned host result tensors.
+
+    ``enqueue`` is the same pass without a place where the host has to wait: it returns a
+    ``PendingPass``.  Passes enqueued one after the other overlap - the uploads of the next one
+    run under the downloads of the one before - so a loop that keeps two passes in flight
+    (enqueue pass i + 1, then ``wait()`` for pass i and consume its results; two sets of result
+    buffers) never leaves a PCIe direction idle while a pass fills or drains."""
 
     def __init__(self, device_index: int = 0, piece_bytes: int = 40 << 20):
         import torch_mojo_backend_b200 as tmb
@@ -32,7 +57,7 @@ class HostAttentionPipeline:
         self.device = torch.device("mojo", self.index)
         self.piece_bytes = int(piece_bytes)   # upload size of one piece; smaller ones cost more in dispatch than the overlap wins
         self._streams = tuple(torch.cuda.Stream(device=self.index) for _ in range(3))
-        self._keep: list = []
+        self._pending: list[PendingPass] = []
 
     # ------------------------------------------------------------------ planning
     def pieces(self, q: torch.Tensor, k: torch.Tensor, with_backward: bool):
@@ -53,10 +78,13 @@ class HostAttentionPipeline:
                 for i in range(B) for g in range(split)]
 
     # ------------------------------------------------------------------ one pass
-    def run(self, q, k, v, dout=None, *, is_causal: bool, scale: float | None = None, out=None, grads=None):
-        """Enqueue one pass; returns ``(out, (dq, dk, dv) or None)`` — pinned host tensors that are
-        complete once ``synchronize()`` has returned.  Pass ``out`` / ``grads`` to reuse result
-        buffers (they must be pinned, e.g. from ``torch_mojo_backend_b200.pinned_empty``)."""
+    def enqueue(self, q, k, v, dout=None, *, is_causal: bool, scale: float | None = None, out=None,
+                grads=None) -> PendingPass:
+        """Enqueue one pass and return at once.  ``out`` / ``grads``: pinned host result tensors to
+        fill (e.g. from ``torch_mojo_backend_b200.pinned_empty``; allocated when omitted); a buffer
+        must not be handed to a new pass before the pass that last wrote it has been waited for.
+        The inputs are host tensors: nothing on the current stream is waited for, except by the
+        first pass after a ``synchronize()``."""
         tmb = self._tmb
         backward = dout is not None
         if out is None:
@@ -65,11 +93,13 @@ class HostAttentionPipeline:
             grads = tuple(tmb.pinned_empty(t.shape, t.dtype) for t in (q, k, v))
         flash_fwd = torch.ops.aten._scaled_dot_product_flash_attention
         flash_bwd = torch.ops.aten._scaled_dot_product_flash_attention_backward
-        main = torch.cuda.current_stream(self.index)
         s_in, s_run, s_out = self._streams
-        for s in self._streams:
-            s.wait_stream(main)
-        keep = self._keep
+        self._pending = [p for p in self._pending if p._done is not None]
+        if not self._pending:
+            main = torch.cuda.current_stream(self.index)
+            for s in self._streams:
+                s.wait_stream(main)
+        keep: list = []
         for bs, qs, ks in self.pieces(q, k, backward):
             with torch.cuda.stream(s_in):
                 dev_in = [q[bs, qs].to(self.device, non_blocking=True), k[bs, ks].to(self.device, non_blocking=True),
@@ -94,14 +124,28 @@ class HostAttentionPipeline:
                 for dst, grad, hs in zip(grads or (), g, (qs, ks, ks)):
                     dst[bs, hs].copy_(grad, non_blocking=True)
             # the three streams use one another's allocations: nothing goes back to the allocator
-            # before synchronize()
+            # before the pass has been waited for
             keep.extend(dev_in)
             keep.extend((o, lse) + tuple(g))
-        for s in self._streams:
-            main.wait_stream(s)
-        return out, (grads if backward else None)
+        done = torch.cuda.Event()
+        done.record(s_out)   # the download stream runs in order: behind this pass's last copy
+        pending = PendingPass(out, grads if backward else None, done, keep)
+        self._pending.append(pending)
+        return pending
+
+    def run(self, q, k, v, dout=None, *, is_causal: bool, scale: float | None = None, out=None, grads=None):
+        """Enqueue one pass; returns ``(out, (dq, dk, dv) or None)`` — pinned host tensors that are
+        complete once ``synchronize()`` has returned."""
+        pending = self.enqueue(q, k, v, dout, is_causal=is_causal, scale=scale, out=out, grads=grads)
+        return pending.out, pending.grads
 
     def synchronize(self) -> None:
-        """Wait for every enqueued pass; the device tensors of those passes are released."""
-        torch.cuda.current_stream(self.index).synchronize()
-        self._keep.clear()
+        """Wait for every enqueued pass (their device tensors are released) and order the current
+        stream behind the pipeline's streams."""
+        main = torch.cuda.current_stream(self.index)
+        for s in self._streams:
+            main.wait_stream(s)
+        for p in self._pending:
+            p.wait()
+        self._pending.clear()
+        main.synchronize()

@@ -140,8 +140,8 @@ class HostAttentionPipeline:
         return pending.out, pending.grads
 
     def synchronize(self) -> None:
-        """Wait for every enqueued pass (their device tensors are released) and order the current
-        stream behind the pipeline's streams."""
+        """Wait for every enqueued pass (their device tensors are released), order the current
+        stream behind the pipeline's streams and raise if a kernel reported a timed-out wait."""
         main = torch.cuda.current_stream(self.index)
         for s in self._streams:
             main.wait_stream(s)
@@ -149,3 +149,7 @@ class HostAttentionPipeline:
             p.wait()
         self._pending.clear()
         main.synchronize()
+        # a kernel that gave up on an internal wait has left its results undefined: say so here
+        from . import flash_ops
+
+        flash_ops.check_status(self.index)

@@ -335,17 +335,30 @@ int bwd_impl(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_tens
   return e == cudaSuccess ? B200FA_OK : B200FA_ERR_CUDA;
 }
 
-// key splits of the split-KV forward: enough CTAs for about two waves, at least 256 keys each
+// Key splits of the split-KV forward.  The partial kernel keeps two 8-warp CTAs per SM (296 at a
+// time on 148 SMs), and a grid runs for about (its waves) x (keys in a split + a fixed cost per
+// CTA worth some 192 keys: prologue, merge of the warps, the partial written and combined).
+// Among the split counts up to 64 with at least 256 keys a split, take the cheapest by that
+// model; the first found wins a tie, which is the one with fewer splits.
 int splitkv_splits(int64_t B, int64_t Hkv, int64_t Sk, int* split_len) {
-  int64_t n = (2 * 148 + B * Hkv - 1) / (B * Hkv);
-  const int64_t max_n = (Sk + 255) / 256;
-  if (n > max_n) n = max_n;
-  if (n < 1) n = 1;
-  if (n > 64) n = 64;
-  int64_t len = ((Sk + n - 1) / n + 63) / 64 * 64;
-  n = (Sk + len - 1) / len;
-  *split_len = static_cast<int>(len);
-  return static_cast<int>(n);
+  const int64_t slots = 2 * 148;
+  int64_t max_n = (Sk + 255) / 256;
+  if (max_n > 64) max_n = 64;
+  if (max_n < 1) max_n = 1;
+  int64_t best_n = 1, best_len = (Sk + 63) / 64 * 64, best_cost = -1;
+  for (int64_t cand = 1; cand <= max_n; ++cand) {
+    const int64_t len = ((Sk + cand - 1) / cand + 63) / 64 * 64;
+    const int64_t n = (Sk + len - 1) / len;
+    const int64_t waves = (B * Hkv * n + slots - 1) / slots;
+    const int64_t cost = waves * (len + 192);
+    if (best_cost < 0 || cost < best_cost) {
+      best_cost = cost;
+      best_n = n;
+      best_len = len;
+    }
+  }
+  *split_len = static_cast<int>(best_len);
+  return static_cast<int>(best_n);
 }
 
 }  // namespace

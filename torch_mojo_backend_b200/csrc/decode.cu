@@ -8,10 +8,17 @@
 // split); the arithmetic is the forward's (fa4_fwd_kernel.mojo:650-861): exp2-domain online
 // softmax with c = scale*log2(e), fp32 accumulation, LSE = max*ln2 + ln(sum).
 //
-// Kernel 1, one CTA per (key split, kv head, batch): rows r = (query head of the group, query
-// row), at most 16 of them.  Per 64-key tile: stage K and V as fp32 in shared memory; scores
-// S[r][key] by threads (r, key); one warp per row does the online-softmax update; thread
-// (r, d) accumulates O[r][d].  Writes (max, sum, O) per split.
+// Kernel 1, one CTA of eight warps per (key split, kv head, batch).  Rows r = (query head of the
+// group, query row), at most 16 of them, at most 8 per warp (more: the warps form two groups).
+// A lane owns D/32 head-dim elements: it holds those of every query row in registers and reads the
+// same elements of each K and V row straight from global memory (a warp reads one 256- or 128-byte
+// row per load instruction: fully coalesced, no shared-memory staging, no block-wide barrier in the
+// loop).  Keys go in blocks of eight, the blocks of a split dealt round-robin to the warps: partial
+// dot products per lane, a reduce-scatter over the lanes that leaves lane L with the score of key
+// L mod 8, the online-softmax update on those, probabilities broadcast back by shuffles for
+// O += P V.  The warps' (max, sum, O) are merged through shared memory at the end.  HBM-bound by
+// design: 2*Sk*D*sizeof(T) bytes per KV head, read once; at 4 rows it needs about 60 instructions
+// per key and warp, inside what four schedulers issue while an SM's share of HBM delivers the key.
 // Kernel 2, one warp per output row: merges the splits, writes out and lse.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -21,18 +28,9 @@
 namespace b200fa {
 namespace {
 
-constexpr int kKeys = 64;       // keys per tile
-constexpr int kMaxRows = 16;    // query rows (group * Sq) one CTA carries
-constexpr int kThreadsDecode = 256;
-
-template <typename T>
-__device__ __forceinline__ float ld_f32(const T* p);
-template <>
-__device__ __forceinline__ float ld_f32<float>(const float* p) { return *p; }
-template <>
-__device__ __forceinline__ float ld_f32<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
-template <>
-__device__ __forceinline__ float ld_f32<__half>(const __half* p) { return __half2float(*p); }
+constexpr int kKeyBlock = 8;        // keys per step of a warp
+constexpr int kWarpsDecode = 8;
+constexpr int kThreadsDecode = kWarpsDecode * 32;
 
 template <typename T>
 __device__ __forceinline__ T st_f32(float x);
@@ -43,143 +41,203 @@ __device__ __forceinline__ __nv_bfloat16 st_f32<__nv_bfloat16>(float x) { return
 template <>
 __device__ __forceinline__ __half st_f32<__half>(float x) { return __float2half_rn(x); }
 
-template <int kD>
-constexpr int decode_smem_bytes() {
-  // K tile [64][D+1], V tile [64][D], Q rows [16][D], scores [16][64], per-row max / sum / correction [3][16]
-  return (kKeys * (kD + 1) + kKeys * kD + kMaxRows * kD + kMaxRows * kKeys + 3 * kMaxRows) * 4;
+// kN consecutive elements (2 or 4) starting at p, as floats, with one vector load
+template <typename T, int kN>
+__device__ __forceinline__ void load_vec(const T* p, float* out);
+template <>
+__device__ __forceinline__ void load_vec<float, 4>(const float* p, float* out) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+}
+template <>
+__device__ __forceinline__ void load_vec<float, 2>(const float* p, float* out) {
+  const float2 v = *reinterpret_cast<const float2*>(p);
+  out[0] = v.x; out[1] = v.y;
+}
+template <>
+__device__ __forceinline__ void load_vec<__nv_bfloat16, 4>(const __nv_bfloat16* p, float* out) {
+  const uint2 v = *reinterpret_cast<const uint2*>(p);
+  out[0] = __uint_as_float(v.x << 16); out[1] = __uint_as_float(v.x & 0xffff0000u);
+  out[2] = __uint_as_float(v.y << 16); out[3] = __uint_as_float(v.y & 0xffff0000u);
+}
+template <>
+__device__ __forceinline__ void load_vec<__nv_bfloat16, 2>(const __nv_bfloat16* p, float* out) {
+  const uint32_t v = *reinterpret_cast<const uint32_t*>(p);
+  out[0] = __uint_as_float(v << 16); out[1] = __uint_as_float(v & 0xffff0000u);
+}
+template <>
+__device__ __forceinline__ void load_vec<__half, 4>(const __half* p, float* out) {
+  const uint2 v = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
+  const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+  out[0] = a.x; out[1] = a.y; out[2] = c.x; out[3] = c.y;
+}
+template <>
+__device__ __forceinline__ void load_vec<__half, 2>(const __half* p, float* out) {
+  const uint32_t v = *reinterpret_cast<const uint32_t*>(p);
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v));
+  out[0] = a.x; out[1] = a.y;
 }
 
-template <typename T, int kD>
-__global__ void __launch_bounds__(kThreadsDecode) splitkv_partial_kernel(const SplitKvParams p) {
-  extern __shared__ float sm[];
-  float* sK = sm;                          // [64][kD+1]
-  float* sV = sK + kKeys * (kD + 1);       // [64][kD]
-  float* sQ = sV + kKeys * kD;             // [rows][kD]
-  float* sS = sQ + kMaxRows * kD;          // [rows][64]: scores, then probabilities
-  float* sM = sS + kMaxRows * kKeys;       // [rows] running max (log2 domain)
-  float* sL = sM + kMaxRows;               // [rows] running sum
-  float* sC = sL + kMaxRows;               // [rows] correction factor of this tile
+// kR: query rows a warp carries (the rows of the problem padded up to 1, 2, 4 or 8)
+template <typename T, int kD, int kR>
+__global__ void __launch_bounds__(kThreadsDecode, kR <= 4 ? 2 : 1) splitkv_partial_kernel(const SplitKvParams p) {
+  constexpr int kDP = kD / 32;   // head-dim elements per lane
+  __shared__ float sMerge[kWarpsDecode][kR][kD + 2];   // per warp and row: O, then max and sum
   const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int group = p.Hq / p.Hkv;
-  const int rows = group * p.Sq;           // <= kMaxRows
+  const int rows = group * p.Sq;                       // <= 16
+  const int ngroups = (rows + kR - 1) / kR;            // 1 or 2 groups of warps, kR rows each
+  const int wpg = kWarpsDecode / ngroups;              // warps that share a group's rows and split its keys
   const int k_begin = split * p.split_len;
   const int k_end = min(p.Sk, k_begin + p.split_len);
-  const float c = p.scale_log2;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int rg = warp / wpg, wi = warp - rg * wpg;
+  const int r0 = rg * kR;
+  const int d0 = lane * kDP;
+  constexpr unsigned kFull = 0xffffffffu;
 
-  // row r <-> query head hk*group + r / Sq, query row r % Sq
-  for (int idx = tid; idx < rows * kD; idx += kThreadsDecode) {
-    const int r = idx / kD, d = idx - r * kD;
-    const int h = hk * group + r / p.Sq, qi = r % p.Sq;
-    const T* q = reinterpret_cast<const T*>(p.q.ptr) + (int64_t)b * p.q.sb + (int64_t)h * p.q.sh + (int64_t)qi * p.q.ss;
-    sQ[idx] = ld_f32<T>(q + d);
-  }
-  if (tid < kMaxRows) {
-    sM[tid] = -INFINITY;
-    sL[tid] = 0.f;
-  }
-  // thread (r, d-slot) owns O[r][d] for d = d-slot, d-slot + stride ...: rows * kD accumulators over 256 threads
-  constexpr int kAccPerThread = kMaxRows * kD / kThreadsDecode;   // 4 (D=64) or 8 (D=128)
-  float acc[kAccPerThread];
+  // this lane's elements of the group's query rows, already multiplied by scale*log2(e)
+  float q[kR][kDP];
+  int q_limit[kR];   // last key a row sees (causal), or the last key of the split
 #pragma unroll
-  for (int i = 0; i < kAccPerThread; ++i) acc[i] = 0.f;
+  for (int r = 0; r < kR; ++r) {
+    const int rr = r0 + r;
+    q_limit[r] = -1;   // a padding row sees nothing
+#pragma unroll
+    for (int e = 0; e < kDP; ++e) q[r][e] = 0.f;
+    if (rr < rows) {
+      const int h = hk * group + rr / p.Sq, qi = rr % p.Sq;
+      const T* qp = reinterpret_cast<const T*>(p.q.ptr) + (int64_t)b * p.q.sb + (int64_t)h * p.q.sh + (int64_t)qi * p.q.ss + d0;
+      load_vec<T, kDP>(qp, q[r]);
+#pragma unroll
+      for (int e = 0; e < kDP; ++e) q[r][e] *= p.scale_log2;
+      q_limit[r] = p.causal ? min(k_end - 1, qi + p.causal_off) : k_end - 1;
+    }
+  }
+  float m[kR], l[kR], o[kR][kDP];
+#pragma unroll
+  for (int r = 0; r < kR; ++r) {
+    m[r] = -INFINITY;
+    l[r] = 0.f;
+#pragma unroll
+    for (int e = 0; e < kDP; ++e) o[r][e] = 0.f;
+  }
+  const T* kbase = reinterpret_cast<const T*>(p.k.ptr) + (int64_t)b * p.k.sb + (int64_t)hk * p.k.sh + d0;
+  const T* vbase = reinterpret_cast<const T*>(p.v.ptr) + (int64_t)b * p.v.sb + (int64_t)hk * p.v.sh + d0;
 
-  for (int n0 = k_begin; n0 < k_end; n0 += kKeys) {
-    __syncthreads();   // the previous tile's K, V and probabilities are no longer read
-    // 16 bytes per load: rows are 16-byte aligned with a unit head_dim stride
-    constexpr int kVec = 16 / static_cast<int>(sizeof(T));
-    for (int idx = tid; idx < kKeys * (kD / kVec); idx += kThreadsDecode) {
-      const int r = idx / (kD / kVec), d = (idx - r * (kD / kVec)) * kVec;
-      const int key = n0 + r;
-      float kf[kVec], vf[kVec];
-      if (key < k_end) {
-        const T* kp = reinterpret_cast<const T*>(p.k.ptr) + (int64_t)b * p.k.sb + (int64_t)hk * p.k.sh + (int64_t)key * p.k.ss + d;
-        const T* vp = reinterpret_cast<const T*>(p.v.ptr) + (int64_t)b * p.v.sb + (int64_t)hk * p.v.sh + (int64_t)key * p.v.ss + d;
-        const uint4 kw = *reinterpret_cast<const uint4*>(kp);
-        const uint4 vw = *reinterpret_cast<const uint4*>(vp);
-        const T* ke = reinterpret_cast<const T*>(&kw);
-        const T* ve = reinterpret_cast<const T*>(&vw);
+  // K and V elements of eight keys: sixteen independent loads, no branch among them (a key past the
+  // end of the split re-reads the split's last key, and its score is masked in `step`)
+  auto load_block = [&](int key0, float (&kf)[kKeyBlock][kDP], float (&vf)[kKeyBlock][kDP]) {
 #pragma unroll
-        for (int e = 0; e < kVec; ++e) {
-          kf[e] = ld_f32<T>(ke + e);
-          vf[e] = ld_f32<T>(ve + e);
+    for (int kk = 0; kk < kKeyBlock; ++kk) {
+      const int key = min(key0 + kk, k_end - 1);
+      load_vec<T, kDP>(kbase + (int64_t)key * p.k.ss, kf[kk]);
+      load_vec<T, kDP>(vbase + (int64_t)key * p.v.ss, vf[kk]);
+    }
+  };
+  auto step = [&](int key0, const float (&kf)[kKeyBlock][kDP], const float (&vf)[kKeyBlock][kDP]) {
+    const int my_key = key0 + (lane & 7);   // the key whose score this lane ends up with
+#pragma unroll
+    for (int r = 0; r < kR; ++r) {
+      // partial dot products over this lane's head-dim elements, eight keys
+      float part[kKeyBlock];
+#pragma unroll
+      for (int kk = 0; kk < kKeyBlock; ++kk) {
+        float2 a2 = __fmul2_rn(make_float2(q[r][0], q[r][1]), make_float2(kf[kk][0], kf[kk][1]));
+        if constexpr (kDP == 4) a2 = __ffma2_rn(make_float2(q[r][2], q[r][3]), make_float2(kf[kk][2], kf[kk][3]), a2);
+        part[kk] = a2.x + a2.y;
+      }
+      // reduce-scatter over lane bits 2, 1, 0: lane L keeps key L & 7; then the four groups of eight lanes are summed
+      float h4[4], h2[2];
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        const bool up = lane & 4;
+        const float keep = up ? part[kk + 4] : part[kk], send = up ? part[kk] : part[kk + 4];
+        h4[kk] = keep + __shfl_xor_sync(kFull, send, 4);
+      }
+#pragma unroll
+      for (int kk = 0; kk < 2; ++kk) {
+        const bool up = lane & 2;
+        const float keep = up ? h4[kk + 2] : h4[kk], send = up ? h4[kk] : h4[kk + 2];
+        h2[kk] = keep + __shfl_xor_sync(kFull, send, 2);
+      }
+      float sc;
+      {
+        const bool up = lane & 1;
+        const float keep = up ? h2[1] : h2[0], send = up ? h2[0] : h2[1];
+        sc = keep + __shfl_xor_sync(kFull, send, 1);
+      }
+      sc += __shfl_xor_sync(kFull, sc, 8);
+      sc += __shfl_xor_sync(kFull, sc, 16);
+      if (my_key > q_limit[r]) sc = -INFINITY;   // masked, past the end, or a padding row
+      // online softmax over the eight keys (log2 domain)
+      float bm = sc;
+      bm = fmaxf(bm, __shfl_xor_sync(kFull, bm, 1));
+      bm = fmaxf(bm, __shfl_xor_sync(kFull, bm, 2));
+      bm = fmaxf(bm, __shfl_xor_sync(kFull, bm, 4));
+      const float m_new = fmaxf(m[r], bm);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;   // nothing visible so far: everything stays zero
+      const float pr = exp2f(sc - m_use);
+      const float corr = exp2f(m[r] - m_use);                   // 0 on the first block with a visible key
+      m[r] = m_new;
+      l[r] = l[r] * corr + (lane < 8 ? pr : 0.f);               // every key once (the four lane groups hold copies)
+#pragma unroll
+      for (int e = 0; e < kDP; ++e) o[r][e] *= corr;
+#pragma unroll
+      for (int kk = 0; kk < kKeyBlock; ++kk) {
+        const float pk = __shfl_sync(kFull, pr, kk);
+        const float2 pk2 = make_float2(pk, pk);
+#pragma unroll
+        for (int e = 0; e < kDP; e += 2) {
+          const float2 t = __ffma2_rn(pk2, make_float2(vf[kk][e], vf[kk][e + 1]), make_float2(o[r][e], o[r][e + 1]));
+          o[r][e] = t.x;
+          o[r][e + 1] = t.y;
         }
-      } else {
-#pragma unroll
-        for (int e = 0; e < kVec; ++e) kf[e] = vf[e] = 0.f;
-      }
-#pragma unroll
-      for (int e = 0; e < kVec; ++e) {
-        sK[r * (kD + 1) + d + e] = kf[e];
-        sV[r * kD + d + e] = vf[e];
       }
     }
-    __syncthreads();
-    // scores, scaled into the log2 domain; masked entries are -inf
-    for (int idx = tid; idx < rows * kKeys; idx += kThreadsDecode) {
-      const int r = idx / kKeys, kk = idx - r * kKeys;
-      const int key = n0 + kk;
-      const int qi = r % p.Sq;
-      float s = 0.f;
-#pragma unroll 8
-      for (int d = 0; d < kD; ++d) s = fmaf(sQ[r * kD + d], sK[kk * (kD + 1) + d], s);
-      const bool masked = key >= k_end || (p.causal && key > qi + p.causal_off);
-      sS[idx] = masked ? -INFINITY : s * c;
-    }
-    __syncthreads();
-    // online softmax: one warp per row (two keys per lane)
-    for (int r = warp; r < rows; r += kThreadsDecode / 32) {
-      const float s0 = sS[r * kKeys + lane], s1 = sS[r * kKeys + 32 + lane];
-      float mx = fmaxf(s0, s1);
+  };
+  const int stride = wpg * kKeyBlock;
+  for (int key0 = k_begin + wi * kKeyBlock; key0 < k_end; key0 += stride) {
+    float kf[kKeyBlock][kDP], vf[kKeyBlock][kDP];
+    load_block(key0, kf, vf);
+    step(key0, kf, vf);
+  }
+  // this warp's results to shared memory
 #pragma unroll
-      for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-      const float m_old = sM[r];
-      float m_new = fmaxf(m_old, mx);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;   // a fully masked row so far: keep everything at zero
-      const float p0 = exp2f(s0 - m_use), p1 = exp2f(s1 - m_use);
-      float sum = p0 + p1;
+  for (int r = 0; r < kR; ++r) {
+    float ls = l[r];
 #pragma unroll
-      for (int o = 16; o >= 1; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-      const float corr = exp2f(m_old - m_use);   // 0 on the first tile that has a visible key
-      sS[r * kKeys + lane] = p0;
-      sS[r * kKeys + 32 + lane] = p1;
-      if (lane == 0) {
-        sM[r] = m_new;
-        sL[r] = sL[r] * corr + sum;
-        sC[r] = corr;
-      }
-    }
-    __syncthreads();
-    // O[r][d] = O[r][d] * corr + sum_key P[r][key] V[key][d]
+    for (int off = 16; off >= 1; off >>= 1) ls += __shfl_xor_sync(kFull, ls, off);
 #pragma unroll
-    for (int i = 0; i < kAccPerThread; ++i) {
-      const int idx = tid + i * kThreadsDecode;
-      const int r = idx / kD, d = idx - r * kD;
-      if (r < rows) {
-        float a = acc[i] * sC[r];
-#pragma unroll 8
-        for (int kk = 0; kk < kKeys; ++kk) a = fmaf(sS[r * kKeys + kk], sV[kk * kD + d], a);
-        acc[i] = a;
-      }
+    for (int e = 0; e < kDP; ++e) sMerge[warp][r][d0 + e] = o[r][e];
+    if (lane == 0) {
+      sMerge[warp][r][kD] = m[r];
+      sMerge[warp][r][kD + 1] = ls;
     }
   }
   __syncthreads();
-  // partial results of this split: (B, Hq, Sq, nsplit, D) and (B, Hq, Sq, nsplit, 2)
-#pragma unroll
-  for (int i = 0; i < kAccPerThread; ++i) {
-    const int idx = tid + i * kThreadsDecode;
-    const int r = idx / kD, d = idx - r * kD;
-    if (r < rows) {
-      const int h = hk * group + r / p.Sq, qi = r % p.Sq;
-      const int64_t row = (((int64_t)b * p.Hq + h) * p.Sq + qi) * p.nsplit + split;
-      p.part_o[row * kD + d] = acc[i];
+  // merge the warps of a group; partial results of this split go to (B, Hq, Sq, nsplit, D) and (B, Hq, Sq, nsplit, 2)
+  for (int idx = tid; idx < ngroups * kR * kD; idx += kThreadsDecode) {
+    const int g = idx / (kR * kD), r = (idx / kD) % kR, d = idx % kD;
+    const int rr = g * kR + r;
+    if (rr >= rows) continue;
+    float mm = -INFINITY;
+    for (int w = 0; w < wpg; ++w) mm = fmaxf(mm, sMerge[g * wpg + w][r][kD]);
+    const float m_use = (mm == -INFINITY) ? 0.f : mm;
+    float acc = 0.f, ls = 0.f;
+    for (int w = 0; w < wpg; ++w) {
+      const float wgt = exp2f(sMerge[g * wpg + w][r][kD] - m_use);
+      acc = fmaf(sMerge[g * wpg + w][r][d], wgt, acc);
+      ls = fmaf(sMerge[g * wpg + w][r][kD + 1], wgt, ls);
     }
-  }
-  if (tid < rows) {
-    const int h = hk * group + tid / p.Sq, qi = tid % p.Sq;
+    const int h = hk * group + rr / p.Sq, qi = rr % p.Sq;
     const int64_t row = (((int64_t)b * p.Hq + h) * p.Sq + qi) * p.nsplit + split;
-    p.part_ml[row * 2] = sM[tid];
-    p.part_ml[row * 2 + 1] = sL[tid];
+    p.part_o[row * kD + d] = acc;
+    if (d == 0) {
+      p.part_ml[row * 2] = mm;
+      p.part_ml[row * 2 + 1] = ls;
+    }
   }
 }
 
@@ -218,18 +276,24 @@ __global__ void __launch_bounds__(256) splitkv_combine_kernel(const SplitKvParam
   if (lane == 0) p.lse[row] = l > 0.f ? m * 0.6931471805599453f + logf(l) : -INFINITY;
 }
 
-template <typename T, int kD>
-cudaError_t launch_t(const SplitKvParams& p, cudaStream_t stream) {
-  constexpr int smem = decode_smem_bytes<kD>();
-  auto k1 = splitkv_partial_kernel<T, kD>;
-  cudaError_t e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (e != cudaSuccess) return e;
-  k1<<<dim3(p.nsplit, p.Hkv, p.B), kThreadsDecode, smem, stream>>>(p);
-  e = cudaGetLastError();
+template <typename T, int kD, int kR>
+cudaError_t launch_rows(const SplitKvParams& p, cudaStream_t stream) {
+  splitkv_partial_kernel<T, kD, kR><<<dim3(p.nsplit, p.Hkv, p.B), kThreadsDecode, 0, stream>>>(p);
+  cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   const int64_t rows = (int64_t)p.B * p.Hq * p.Sq;
   splitkv_combine_kernel<T, kD><<<(unsigned)((rows * 32 + 255) / 256), 256, 0, stream>>>(p);
   return cudaGetLastError();
+}
+
+template <typename T, int kD>
+cudaError_t launch_t(const SplitKvParams& p, cudaStream_t stream) {
+  // rows a warp carries: those of the problem, padded to a power of two, at most 8 (9-16 rows: two groups of warps)
+  const int rows = (p.Hq / p.Hkv) * p.Sq;
+  if (rows <= 1) return launch_rows<T, kD, 1>(p, stream);
+  if (rows <= 2) return launch_rows<T, kD, 2>(p, stream);
+  if (rows <= 4) return launch_rows<T, kD, 4>(p, stream);
+  return launch_rows<T, kD, 8>(p, stream);
 }
 
 }  // namespace

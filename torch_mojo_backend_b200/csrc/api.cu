@@ -335,13 +335,14 @@ int bwd_impl(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_tens
   return e == cudaSuccess ? B200FA_OK : B200FA_ERR_CUDA;
 }
 
-// Key splits of the split-KV forward.  The partial kernel keeps two 8-warp CTAs per SM (296 at a
-// time on 148 SMs), and a grid runs for about (its waves) x (keys in a split + a fixed cost per
-// CTA worth some 192 keys: prologue, merge of the warps, the partial written and combined).
-// Among the split counts up to 64 with at least 256 keys a split, take the cheapest by that
-// model; the first found wins a tie, which is the one with fewer splits.
-int splitkv_splits(int64_t B, int64_t Hkv, int64_t Sk, int* split_len) {
-  const int64_t slots = 2 * 148;
+// Key splits of the split-KV forward.  The partial kernel keeps three 4-warp CTAs per SM (444 at
+// a time on 148 SMs) when a KV head has up to eight query rows, two with more, and a grid runs
+// for about (its waves) x (keys in a split + a fixed cost per CTA worth some 192 keys: prologue,
+// merge of the warps, the partial written and combined).  Among the split counts up to 64 with
+// at least 256 keys a split, take the cheapest by that model; the first found wins a tie, which
+// is the one with fewer splits.
+int splitkv_splits(int64_t B, int64_t Hkv, int64_t rows, int64_t Sk, int* split_len) {
+  const int64_t slots = (rows <= 8 ? 3 : 2) * 148;
   int64_t max_n = (Sk + 255) / 256;
   if (max_n > 64) max_n = 64;
   if (max_n < 1) max_n = 1;
@@ -489,7 +490,7 @@ size_t b200fa_fwd_splitkv_workspace_bytes(int64_t batch, int64_t heads_q, int64_
                                           int64_t seqlen_k, int64_t head_dim) {
   if (batch <= 0 || heads_q <= 0 || heads_kv <= 0 || seqlen_q <= 0 || seqlen_k <= 0 || head_dim <= 0) return 0;
   int split_len = 0;
-  const int n = splitkv_splits(batch, heads_kv, seqlen_k, &split_len);
+  const int n = splitkv_splits(batch, heads_kv, heads_q / heads_kv * seqlen_q, seqlen_k, &split_len);
   const size_t rows = static_cast<size_t>(batch) * heads_q * seqlen_q * n;
   return align256(rows * head_dim * 4) + align256(rows * 2 * 4);
 }
@@ -521,7 +522,7 @@ int b200fa_fwd_splitkv(const b200fa_tensor4* q, const b200fa_tensor4* k, const b
   const size_t need = b200fa_fwd_splitkv_workspace_bytes(B, Hq, Hkv, Sq, Sk, D);
   if (!workspace || workspace_bytes < need || reinterpret_cast<uintptr_t>(workspace) % 256 != 0)
     return B200FA_ERR_WORKSPACE;
-  p.nsplit = splitkv_splits(B, Hkv, Sk, &p.split_len);
+  p.nsplit = splitkv_splits(B, Hkv, Hq / Hkv * Sq, Sk, &p.split_len);
   const size_t rows = static_cast<size_t>(B) * Hq * Sq * p.nsplit;
   p.part_o = reinterpret_cast<float*>(workspace);
   p.part_ml = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + align256(rows * D * 4));

@@ -8,17 +8,21 @@
 // split); the arithmetic is the forward's (fa4_fwd_kernel.mojo:650-861): exp2-domain online
 // softmax with c = scale*log2(e), fp32 accumulation, LSE = max*ln2 + ln(sum).
 //
-// Kernel 1, one CTA of eight warps per (key split, kv head, batch).  Rows r = (query head of the
-// group, query row), at most 16 of them, at most 8 per warp (more: the warps form two groups).
-// A lane owns D/32 head-dim elements: it holds those of every query row in registers and reads the
-// same elements of each K and V row straight from global memory (a warp reads one 256- or 128-byte
-// row per load instruction: fully coalesced, no shared-memory staging, no block-wide barrier in the
-// loop).  Keys go in blocks of eight, the blocks of a split dealt round-robin to the warps: partial
-// dot products per lane, a reduce-scatter over the lanes that leaves lane L with the score of key
-// L mod 8, the online-softmax update on those, probabilities broadcast back by shuffles for
-// O += P V.  The warps' (max, sum, O) are merged through shared memory at the end.  HBM-bound by
-// design: 2*Sk*D*sizeof(T) bytes per KV head, read once; at 4 rows it needs about 60 instructions
-// per key and warp, inside what four schedulers issue while an SM's share of HBM delivers the key.
+// Kernel 1, one CTA per (key split, kv head, batch).  Rows r = (query head of the group, query
+// row), at most 16 of them.  K and V rows go from global memory straight to registers, coalesced,
+// with no shared-memory staging and no block-wide barrier in the loop; the warps' (max, sum, O) are
+// merged through shared memory at the end.  HBM-bound by design: 2*Sk*D*sizeof(T) bytes per KV head,
+// read once.  Two forms:
+//   * 16-bit inputs: splitkv_partial_mma_kernel, four warps, 16 keys a step on the warp-level
+//     tensor-core path (described at the kernel);
+//   * fp32 inputs: splitkv_partial_kernel, eight warps, at most 8 rows per warp (more: the warps form
+//     two groups).  A lane owns D/32 head-dim elements: it holds those of every query row in registers
+//     and reads the same elements of each K and V row.  Keys go in blocks of eight, dealt round-robin
+//     to the warps: partial dot products per lane, a reduce-scatter over the lanes that leaves lane L
+//     with the score of key L mod 8, the online-softmax update on those, probabilities broadcast back
+//     by shuffles for O += P V.  About 90 instructions per key and warp at 4 rows: the schedulers, not
+//     HBM, bound it (measured with 16-bit inputs before the tensor-core form existed: 0.55 of the copy
+//     rate, issue slots 59 % busy).
 // Kernel 2, one warp per output row: merges the splits, writes out and lse.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -241,6 +245,250 @@ __global__ void __launch_bounds__(kThreadsDecode, kR <= 4 ? 2 : 1) splitkv_parti
   }
 }
 
+// ---- 16-bit inputs: the same pass on the warp-level tensor-core path ------------------------------
+// For bf16/fp16 the scalar kernel above spends some 90 instructions per key and warp on conversions,
+// dot products and shuffles, and the schedulers, not HBM, bound it.  Here a warp takes 16 keys a step
+// and computes S^T = K Q^T and O^T += V^T P^T with mma.sync m16n8k16 (fp32 accumulation): keys (then
+// head-dim elements) are the M dimension, the query rows the N dimension (8 a tile, kNT tiles), so no
+// tensor-core row is padding.  Operands go from global memory to the fragment registers directly:
+//   * the contraction index of S^T is the head dimension, and any permutation of it may be used as
+//     long as K and Q use the same one.  Thread (g = lane/4, t = lane%4) reads 16 bytes at offset
+//     (4i + t) * 16 of key rows g and g+8 (i = 0 .. D/32-1; the four t of a row read 64 contiguous
+//     bytes per instruction) and the same bytes of query row g; the two halves of such a 16-byte piece
+//     are the two 8-byte fragments of one k16 step.
+//   * O^T's M index is a head-dim element.  Thread (g, t) reads 16 bytes at offset 128h + 16g of V
+//     rows 2t, 2t+1, 2t+8, 2t+9 (the eight g of a row read 128 contiguous bytes); register q of such
+//     a piece holds elements d and d+1 of its key, and a byte permute of the registers of two
+//     neighbouring keys makes the (key, key+1) pairs the A fragment wants, for M slot g (element d)
+//     and slot g+8 (element d+1) of tile (h, q).
+//   * P^T (keys x rows) comes out of the softmax as an accumulator fragment (key g, rows 2t, 2t+1);
+//     movmatrix transposes the packed 8x8 tiles into the B fragment (keys 2t, 2t+1; row g).
+// A thread owns query rows 2t and 2t+1 of each tile: their running max is reduced over the eight g
+// lanes by three shuffles, their sums stay per-thread until the end.  Loads of the next step's K are
+// issued as soon as the current K fragments are consumed, V's likewise, so a warp has 16 KB (D=128)
+// in flight most of the time.
+constexpr int kMmaKeys = 16;
+constexpr int kMmaWarps = 4;
+
+template <typename T>
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1);
+template <>
+__device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                        uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma16816<__half>(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                                 uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+  const __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
+}
+__device__ __forceinline__ uint32_t reg_of(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
+
+// kNT: tiles of eight query rows (1 or 2)
+template <typename T, int kD, int kNT>
+__global__ void __launch_bounds__(kMmaWarps * 32, kNT == 1 ? 3 : 2) splitkv_partial_mma_kernel(const SplitKvParams p) {
+  constexpr int kKL = kD / 32;   // 16-byte pieces of a K (and Q) row per thread
+  constexpr int kVL = kD / 64;   // 16-byte pieces of a V row per thread
+  constexpr int kRows = 8 * kNT;
+  constexpr unsigned kFull = 0xffffffffu;
+  __shared__ float sMerge[kMmaWarps][kRows][kD + 2];   // per warp and row: O, then max and sum
+  const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int group = p.Hq / p.Hkv;
+  const int rows = group * p.Sq;   // <= 8 * kNT
+  const int k_begin = split * p.split_len;
+  const int k_end = min(p.Sk, k_begin + p.split_len);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+
+  // Q^T fragments: query row 8n + g, the bytes this thread also reads of a K row
+  uint4 qf[kNT][kKL];
+#pragma unroll
+  for (int n = 0; n < kNT; ++n) {
+    const int rr = 8 * n + g;
+#pragma unroll
+    for (int i = 0; i < kKL; ++i) qf[n][i] = make_uint4(0, 0, 0, 0);
+    if (rr < rows) {
+      const int h = hk * group + rr / p.Sq, qi = rr % p.Sq;
+      const T* qp = reinterpret_cast<const T*>(p.q.ptr) + (int64_t)b * p.q.sb + (int64_t)h * p.q.sh + (int64_t)qi * p.q.ss;
+#pragma unroll
+      for (int i = 0; i < kKL; ++i) qf[n][i] = *reinterpret_cast<const uint4*>(qp + (4 * i + t) * 8);
+    }
+  }
+  // rows 2t and 2t+1 of each tile are this thread's in the softmax: the last key each of them sees
+  int q_limit[kNT][2];
+#pragma unroll
+  for (int n = 0; n < kNT; ++n)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int rr = 8 * n + 2 * t + e;
+      const int qi = rr % p.Sq;
+      q_limit[n][e] = rr >= rows ? -1 : (p.causal ? min(k_end - 1, qi + p.causal_off) : k_end - 1);
+    }
+  float m[kNT][2], l[kNT][2];
+  float o[kNT][kVL * 4][4];   // O^T tiles (h, q): [0] (d, row 2t) [1] (d, row 2t+1) [2] (d+1, row 2t) [3] (d+1, row 2t+1)
+#pragma unroll
+  for (int n = 0; n < kNT; ++n) {
+    m[n][0] = m[n][1] = -INFINITY;
+    l[n][0] = l[n][1] = 0.f;
+#pragma unroll
+    for (int j = 0; j < kVL * 4; ++j) o[n][j][0] = o[n][j][1] = o[n][j][2] = o[n][j][3] = 0.f;
+  }
+  const T* kbase = reinterpret_cast<const T*>(p.k.ptr) + (int64_t)b * p.k.sb + (int64_t)hk * p.k.sh + t * 8;
+  const T* vbase = reinterpret_cast<const T*>(p.v.ptr) + (int64_t)b * p.v.sb + (int64_t)hk * p.v.sh + g * 8;
+  const int last = k_end - 1;
+  uint4 kf[2][kKL];   // key rows g, g+8
+  uint4 vf[4][kVL];   // key rows 2t, 2t+1, 2t+8, 2t+9
+  // a key past the end of the split re-reads the split's last key; its score is masked
+  auto load_k = [&](int key0) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const T* row = kbase + (int64_t)min(key0 + g + 8 * r, last) * p.k.ss;
+#pragma unroll
+      for (int i = 0; i < kKL; ++i) kf[r][i] = __ldg(reinterpret_cast<const uint4*>(row + i * 32));
+    }
+  };
+  auto load_v = [&](int key0) {
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const T* row = vbase + (int64_t)min(key0 + 2 * t + (r & 1) + 8 * (r >> 1), last) * p.v.ss;
+#pragma unroll
+      for (int h = 0; h < kVL; ++h) vf[r][h] = __ldg(reinterpret_cast<const uint4*>(row + h * 64));
+    }
+  };
+  const int stride = kMmaWarps * kMmaKeys;
+  int key0 = k_begin + warp * kMmaKeys;
+  if (key0 < k_end) {
+    load_k(key0);
+    load_v(key0);
+  }
+  for (; key0 < k_end; key0 += stride) {
+    // S^T (16 keys x rows): [0] (key g, row 2t) [1] (key g, row 2t+1) [2] (key g+8, row 2t) [3] (key g+8, row 2t+1)
+    float s[kNT][4];
+#pragma unroll
+    for (int n = 0; n < kNT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll
+    for (int i = 0; i < kKL; ++i)
+#pragma unroll
+      for (int half = 0; half < 2; ++half)
+#pragma unroll
+        for (int n = 0; n < kNT; ++n)
+          mma16816<T>(s[n], reg_of(kf[0][i], 2 * half), reg_of(kf[1][i], 2 * half), reg_of(kf[0][i], 2 * half + 1),
+                      reg_of(kf[1][i], 2 * half + 1), reg_of(qf[n][i], 2 * half), reg_of(qf[n][i], 2 * half + 1));
+    load_k(key0 + stride);
+    uint32_t pb[kNT][2];
+#pragma unroll
+    for (int n = 0; n < kNT; ++n) {
+      float corr[2];
+      float pr[4];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        float s_lo = s[n][e] * p.scale_log2, s_hi = s[n][2 + e] * p.scale_log2;
+        if (key0 + g > q_limit[n][e]) s_lo = -INFINITY;   // masked, past the end, or a padding row
+        if (key0 + g + 8 > q_limit[n][e]) s_hi = -INFINITY;
+        float bm = fmaxf(s_lo, s_hi);
+        bm = fmaxf(bm, __shfl_xor_sync(kFull, bm, 4));
+        bm = fmaxf(bm, __shfl_xor_sync(kFull, bm, 8));
+        bm = fmaxf(bm, __shfl_xor_sync(kFull, bm, 16));
+        const float m_new = fmaxf(m[n][e], bm);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;   // nothing visible so far: everything stays zero
+        corr[e] = exp2f(m[n][e] - m_use);                         // 0 on the first step with a visible key
+        pr[e] = exp2f(s_lo - m_use);
+        pr[2 + e] = exp2f(s_hi - m_use);
+        m[n][e] = m_new;
+        l[n][e] = l[n][e] * corr[e] + pr[e] + pr[2 + e];          // this thread's two keys; summed over g at the end
+      }
+#pragma unroll
+      for (int j = 0; j < kVL * 4; ++j) {
+        o[n][j][0] *= corr[0];
+        o[n][j][1] *= corr[1];
+        o[n][j][2] *= corr[0];
+        o[n][j][3] *= corr[1];
+      }
+      pb[n][0] = movmatrix_trans(pack2<T>(pr[0], pr[1]));   // keys 2t, 2t+1 of row g
+      pb[n][1] = movmatrix_trans(pack2<T>(pr[2], pr[3]));   // keys 2t+8, 2t+9 of row g
+    }
+#pragma unroll
+    for (int h = 0; h < kVL; ++h)
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const uint32_t a0 = __byte_perm(reg_of(vf[0][h], q), reg_of(vf[1][h], q), 0x5410);   // element d of keys 2t, 2t+1
+        const uint32_t a1 = __byte_perm(reg_of(vf[0][h], q), reg_of(vf[1][h], q), 0x7632);   // element d+1
+        const uint32_t a2 = __byte_perm(reg_of(vf[2][h], q), reg_of(vf[3][h], q), 0x5410);   // keys 2t+8, 2t+9
+        const uint32_t a3 = __byte_perm(reg_of(vf[2][h], q), reg_of(vf[3][h], q), 0x7632);
+#pragma unroll
+        for (int n = 0; n < kNT; ++n) mma16816<T>(o[n][h * 4 + q], a0, a1, a2, a3, pb[n][0], pb[n][1]);
+      }
+    load_v(key0 + stride);
+  }
+  // this warp's results to shared memory: element d = 64h + 8g + 2q (and d+1) of rows 2t, 2t+1
+#pragma unroll
+  for (int n = 0; n < kNT; ++n) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      float ls = l[n][e];
+      ls += __shfl_xor_sync(kFull, ls, 4);
+      ls += __shfl_xor_sync(kFull, ls, 8);
+      ls += __shfl_xor_sync(kFull, ls, 16);
+      const int r = 8 * n + 2 * t + e;
+#pragma unroll
+      for (int j = 0; j < kVL * 4; ++j) {
+        const int d = 64 * (j >> 2) + 8 * g + 2 * (j & 3);
+        sMerge[warp][r][d] = o[n][j][e];
+        sMerge[warp][r][d + 1] = o[n][j][2 + e];
+      }
+      if (g == 0) {
+        sMerge[warp][r][kD] = m[n][e];
+        sMerge[warp][r][kD + 1] = ls;
+      }
+    }
+  }
+  __syncthreads();
+  // merge the warps; partial results of this split go to (B, Hq, Sq, nsplit, D) and (B, Hq, Sq, nsplit, 2)
+  for (int idx = tid; idx < rows * kD; idx += kMmaWarps * 32) {
+    const int r = idx / kD, d = idx % kD;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kMmaWarps; ++w) mm = fmaxf(mm, sMerge[w][r][kD]);
+    const float m_use = (mm == -INFINITY) ? 0.f : mm;
+    float acc = 0.f, ls = 0.f;
+#pragma unroll
+    for (int w = 0; w < kMmaWarps; ++w) {
+      const float wgt = exp2f(sMerge[w][r][kD] - m_use);
+      acc = fmaf(sMerge[w][r][d], wgt, acc);
+      ls = fmaf(sMerge[w][r][kD + 1], wgt, ls);
+    }
+    const int h = hk * group + r / p.Sq, qi = r % p.Sq;
+    const int64_t row = (((int64_t)b * p.Hq + h) * p.Sq + qi) * p.nsplit + split;
+    p.part_o[row * kD + d] = acc;
+    if (d == 0) {
+      p.part_ml[row * 2] = mm;
+      p.part_ml[row * 2 + 1] = ls;
+    }
+  }
+}
+
 // one warp per (b, h, query row): merge the splits
 template <typename T, int kD>
 __global__ void __launch_bounds__(256) splitkv_combine_kernel(const SplitKvParams p) {
@@ -286,14 +534,29 @@ cudaError_t launch_rows(const SplitKvParams& p, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
+template <typename T, int kD, int kNT>
+cudaError_t launch_mma(const SplitKvParams& p, cudaStream_t stream) {
+  splitkv_partial_mma_kernel<T, kD, kNT><<<dim3(p.nsplit, p.Hkv, p.B), kMmaWarps * 32, 0, stream>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  const int64_t rows = (int64_t)p.B * p.Hq * p.Sq;
+  splitkv_combine_kernel<T, kD><<<(unsigned)((rows * 32 + 255) / 256), 256, 0, stream>>>(p);
+  return cudaGetLastError();
+}
+
 template <typename T, int kD>
 cudaError_t launch_t(const SplitKvParams& p, cudaStream_t stream) {
-  // rows a warp carries: those of the problem, padded to a power of two, at most 8 (9-16 rows: two groups of warps)
   const int rows = (p.Hq / p.Hkv) * p.Sq;
-  if (rows <= 1) return launch_rows<T, kD, 1>(p, stream);
-  if (rows <= 2) return launch_rows<T, kD, 2>(p, stream);
-  if (rows <= 4) return launch_rows<T, kD, 4>(p, stream);
-  return launch_rows<T, kD, 8>(p, stream);
+  if constexpr (sizeof(T) == 2) {
+    // 16-bit inputs: the tensor-core kernel, one or two tiles of eight query rows
+    return rows <= 8 ? launch_mma<T, kD, 1>(p, stream) : launch_mma<T, kD, 2>(p, stream);
+  } else {
+    // fp32: rows a warp carries, padded to a power of two, at most 8 (9-16 rows: two groups of warps)
+    if (rows <= 1) return launch_rows<T, kD, 1>(p, stream);
+    if (rows <= 2) return launch_rows<T, kD, 2>(p, stream);
+    if (rows <= 4) return launch_rows<T, kD, 4>(p, stream);
+    return launch_rows<T, kD, 8>(p, stream);
+  }
 }
 
 }  // namespace

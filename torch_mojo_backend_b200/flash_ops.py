@@ -33,15 +33,12 @@ _SPLITKV_MIN_KEYS = 512
 
 
 def _decode_shaped(batch: int, heads_q: int, heads_kv: int, seq_q: int, seq_k: int) -> bool:
-    """A forward that the split-KV kernels serve faster than the prefill kernel: few query rows per
-    KV head over a long key sequence.  Up to 8 rows one warp carries them all and the kernels run
-    at half of HBM speed or better; with 9-16 rows (two groups of warps, a quarter of that speed) the
-    prefill kernel wins as soon as it has a thread block for every SM (measured on B200: B16 Hq32
-    Hkv8 Sq4 Sk16384, 1.11 ms against 0.75)."""
+    """A forward that the split-KV kernels serve faster than the prefill kernel: at most 16 query
+    rows per KV head over a long key sequence.  The split-KV pass reads K and V once per KV head at
+    0.8-1.0 of the HBM copy rate whatever the row count (measured on B200: B16 Hq32 Hkv8 Sq4
+    Sk16384, 0.19 ms against the prefill kernel's 0.75)."""
     rows = (heads_q // heads_kv) * seq_q
-    if seq_k < _SPLITKV_MIN_KEYS or rows > _lib.SPLITKV_MAX_ROWS:
-        return False
-    return rows <= 8 or batch * heads_q < 148
+    return seq_k >= _SPLITKV_MIN_KEYS and rows <= _lib.SPLITKV_MAX_ROWS
 
 
 def _log(msg: str) -> None:

@@ -150,11 +150,12 @@ void b200fa_dropout_bytes_host(uint64_t philox_seed, uint64_t philox_offset, int
 /*
  * Forward for short query blocks against a long key/value sequence (decode): the key sequence
  * is split over many thread blocks, each streams its share of K and V once for every query
- * head of the GQA group and every query row, and a second kernel merges the partial softmax
- * results.  Needs (Hq / Hkv) * Sq <= B200FA_SPLITKV_MAX_ROWS; any dtype; same out / lse
+ * head of the GQA group and every query row, and the last block of a KV head to finish merges
+ * the partial softmax results (one kernel launch, preceded by a memset of the workspace's
+ * counters on the same stream).  Needs (Hq / Hkv) * Sq <= B200FA_SPLITKV_MAX_ROWS; any dtype; same out / lse
  * contract as b200fa_fwd.  `workspace`: b200fa_fwd_splitkv_workspace_bytes(...) bytes of
  * caller-owned device scratch, 256-byte aligned (fp32 partial outputs and (max, sum) pairs per
- * split).  Takes the place of the reference's single-kernel decode path
+ * split, one counter per KV head); calls that overlap on the GPU need workspaces of their own.  Takes the place of the reference's single-kernel decode path
  * (torch_mojo_backend/eager_kernels/aten_fast.py:9171-9203: q_len == 1, kv_len <= 4096).
  */
 #define B200FA_SPLITKV_MAX_ROWS 16

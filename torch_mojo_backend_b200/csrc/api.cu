@@ -492,7 +492,7 @@ size_t b200fa_fwd_splitkv_workspace_bytes(int64_t batch, int64_t heads_q, int64_
   int split_len = 0;
   const int n = splitkv_splits(batch, heads_kv, heads_q / heads_kv * seqlen_q, seqlen_k, &split_len);
   const size_t rows = static_cast<size_t>(batch) * heads_q * seqlen_q * n;
-  return align256(rows * head_dim * 4) + align256(rows * 2 * 4);
+  return align256(rows * head_dim * 4) + align256(rows * 2 * 4) + align256(static_cast<size_t>(batch) * heads_kv * 4);
 }
 
 int b200fa_fwd_splitkv(const b200fa_tensor4* q, const b200fa_tensor4* k, const b200fa_tensor4* v,
@@ -526,6 +526,7 @@ int b200fa_fwd_splitkv(const b200fa_tensor4* q, const b200fa_tensor4* k, const b
   const size_t rows = static_cast<size_t>(B) * Hq * Sq * p.nsplit;
   p.part_o = reinterpret_cast<float*>(workspace);
   p.part_ml = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + align256(rows * D * 4));
+  p.counters = reinterpret_cast<unsigned*>(static_cast<uint8_t*>(workspace) + align256(rows * D * 4) + align256(rows * 2 * 4));
   p.lse = lse;
   p.B = static_cast<int>(B); p.Hq = static_cast<int>(Hq); p.Hkv = static_cast<int>(Hkv);
   p.Sq = static_cast<int>(Sq); p.Sk = static_cast<int>(Sk); p.D = static_cast<int>(D);

@@ -60,6 +60,7 @@ struct SplitKvParams {
   float* lse;
   float* part_o;    // workspace: (B, Hq, Sq, nsplit, D) fp32
   float* part_ml;   // workspace: (B, Hq, Sq, nsplit, 2) fp32: running max (log2 domain), row sum
+  unsigned* counters;   // workspace: (B, Hkv) splits finished so far, zeroed before the launch
   int B, Hq, Hkv, Sq, Sk, D;
   int causal, causal_off;
   int nsplit, split_len;   // keys per split (a multiple of 64)

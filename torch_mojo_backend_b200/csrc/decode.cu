@@ -2,13 +2,13 @@
 // key/value cache).  The prefill kernel gives such a problem one 256-row CTA per (batch, head)
 // with a handful of useful rows in it; here the key sequence is split over many CTAs so that
 // the whole GPU streams K and V, which are read from HBM once per KV head (all query heads of
-// a GQA group and all query rows share the pass), and a second kernel merges the partial
-// softmax results.  The reference serves this case with a separate single-kernel decode path
+// a GQA group and all query rows share the pass), and the last CTA of a KV head to finish merges
+// the partial softmax results, in the same launch.  The reference serves this case with a separate single-kernel decode path
 // (torch_mojo_backend/eager_kernels/aten_fast.py:9171-9203: q_len == 1, kv_len <= 4096, no
 // split); the arithmetic is the forward's (fa4_fwd_kernel.mojo:650-861): exp2-domain online
 // softmax with c = scale*log2(e), fp32 accumulation, LSE = max*ln2 + ln(sum).
 //
-// Kernel 1, one CTA per (key split, kv head, batch).  Rows r = (query head of the group, query
+// One CTA per (key split, kv head, batch).  Rows r = (query head of the group, query
 // row), at most 16 of them.  K and V rows go from global memory straight to registers, coalesced,
 // with no shared-memory staging and no block-wide barrier in the loop; the warps' (max, sum, O) are
 // merged through shared memory at the end.  HBM-bound by design: 2*Sk*D*sizeof(T) bytes per KV head,
@@ -23,7 +23,7 @@
 //     by shuffles for O += P V.  About 90 instructions per key and warp at 4 rows: the schedulers, not
 //     HBM, bound it (measured with 16-bit inputs before the tensor-core form existed: 0.55 of the copy
 //     rate, issue slots 59 % busy).
-// Kernel 2, one warp per output row: merges the splits, writes out and lse.
+// The merge (finish_split): one warp per output row combines the splits, writes out and lse.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -58,29 +58,91 @@ __device__ __forceinline__ void load_vec<float, 2>(const float* p, float* out) {
   const float2 v = *reinterpret_cast<const float2*>(p);
   out[0] = v.x; out[1] = v.y;
 }
-template <>
-__device__ __forceinline__ void load_vec<__nv_bfloat16, 4>(const __nv_bfloat16* p, float* out) {
-  const uint2 v = *reinterpret_cast<const uint2*>(p);
-  out[0] = __uint_as_float(v.x << 16); out[1] = __uint_as_float(v.x & 0xffff0000u);
-  out[2] = __uint_as_float(v.y << 16); out[3] = __uint_as_float(v.y & 0xffff0000u);
-}
-template <>
-__device__ __forceinline__ void load_vec<__nv_bfloat16, 2>(const __nv_bfloat16* p, float* out) {
-  const uint32_t v = *reinterpret_cast<const uint32_t*>(p);
-  out[0] = __uint_as_float(v << 16); out[1] = __uint_as_float(v & 0xffff0000u);
-}
-template <>
-__device__ __forceinline__ void load_vec<__half, 4>(const __half* p, float* out) {
-  const uint2 v = *reinterpret_cast<const uint2*>(p);
-  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
-  const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
-  out[0] = a.x; out[1] = a.y; out[2] = c.x; out[3] = c.y;
-}
-template <>
-__device__ __forceinline__ void load_vec<__half, 2>(const __half* p, float* out) {
-  const uint32_t v = *reinterpret_cast<const uint32_t*>(p);
-  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v));
-  out[0] = a.x; out[1] = a.y;
+// The last CTA of a (batch, kv head) to finish merges that head's splits: every CTA publishes its
+// partial results (fence), then bumps the head's counter; the one that sees nsplit - 1 owns the
+// merge.  No CTA waits for another.
+template <typename T, int kD>
+__device__ __forceinline__ void finish_split(const SplitKvParams& p, int b, int hk, int rows, int tid, int nthreads) {
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned prev = atomicAdd(p.counters + (int64_t)b * p.Hkv + hk, 1u);
+    s_last = prev == static_cast<unsigned>(p.nsplit - 1);
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  // All rows at once: nthreads / (rows padded to a power of two) threads per row, each with a
+  // contiguous slice of the head dimension, so that few loads depend on one another (the merge runs
+  // while other CTAs still saturate HBM, and a load takes a while).  The partials were written by
+  // other SMs: read them from L2.
+  int rows_pad = 1;
+  while (rows_pad < rows) rows_pad <<= 1;
+  const int tpr = nthreads / rows_pad;           // threads per row: 8 .. 256
+  const int rr = tid / tpr, part = tid % tpr;
+  if (rr >= rows) return;
+  const int group = p.Hq / p.Hkv;
+  const int h = hk * group + rr / p.Sq, qi = rr % p.Sq;
+  const int64_t row = ((int64_t)b * p.Hq + h) * p.Sq + qi;
+  const float2* ml = reinterpret_cast<const float2*>(p.part_ml) + row * p.nsplit;
+  float m = -INFINITY;
+#pragma unroll 8
+  for (int sp = 0; sp < p.nsplit; ++sp) m = fmaxf(m, __ldcg(ml + sp).x);
+  const float m_use = (m == -INFINITY) ? 0.f : m;
+  T* out = reinterpret_cast<T*>(p.out.ptr) + (int64_t)b * p.out.sb + (int64_t)h * p.out.sh + (int64_t)qi * p.out.ss;
+  float l = 0.f;
+  if (tpr * 4 <= kD) {
+    // 4, 8 or 16 elements per thread, in float4 pieces dealt round-robin to the row's threads
+    constexpr int kMaxVec = kD / 4 / 8;            // pieces per thread at 8 threads per row
+    const int nvec = kD / 4 / tpr;                 // 1 .. kMaxVec
+    float4 o[kMaxVec];
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i) o[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4* po = reinterpret_cast<const float4*>(p.part_o + row * p.nsplit * kD) + part;
+#pragma unroll 4
+    for (int sp = 0; sp < p.nsplit; ++sp) {
+      const float2 v = __ldcg(ml + sp);
+      const float w = exp2f(v.x - m_use);          // 0 for a split that saw no visible key
+      l = fmaf(v.y, w, l);
+#pragma unroll
+      for (int i = 0; i < kMaxVec; ++i) {
+        if (i < nvec) {
+          const float4 x = __ldcg(po + sp * (kD / 4) + i * tpr);
+          o[i].x = fmaf(x.x, w, o[i].x); o[i].y = fmaf(x.y, w, o[i].y);
+          o[i].z = fmaf(x.z, w, o[i].z); o[i].w = fmaf(x.w, w, o[i].w);
+        }
+      }
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;     // a row that saw no key at all: 0 with lse -inf
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i) {
+      if (i < nvec) {
+        T* dst = out + (part + i * tpr) * 4;
+        dst[0] = st_f32<T>(o[i].x * inv); dst[1] = st_f32<T>(o[i].y * inv);
+        dst[2] = st_f32<T>(o[i].z * inv); dst[3] = st_f32<T>(o[i].w * inv);
+      }
+    }
+  } else {
+    // more threads than float4 pieces: one or two elements per thread (or none)
+    const int per = tpr >= kD ? 1 : kD / tpr;      // 1 or 2
+    const int d0 = part * per;
+    if (d0 >= kD) return;
+    float o0 = 0.f, o1 = 0.f;
+    const float* po = p.part_o + row * p.nsplit * kD + d0;
+#pragma unroll 4
+    for (int sp = 0; sp < p.nsplit; ++sp) {
+      const float2 v = __ldcg(ml + sp);
+      const float w = exp2f(v.x - m_use);
+      l = fmaf(v.y, w, l);
+      o0 = fmaf(__ldcg(po + (int64_t)sp * kD), w, o0);
+      if (per == 2) o1 = fmaf(__ldcg(po + (int64_t)sp * kD + 1), w, o1);
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    out[d0] = st_f32<T>(o0 * inv);
+    if (per == 2) out[d0 + 1] = st_f32<T>(o1 * inv);
+  }
+  if (part == 0) p.lse[row] = l > 0.f ? m * 0.6931471805599453f + logf(l) : -INFINITY;
 }
 
 // kR: query rows a warp carries (the rows of the problem padded up to 1, 2, 4 or 8)
@@ -243,6 +305,7 @@ __global__ void __launch_bounds__(kThreadsDecode, kR <= 4 ? 2 : 1) splitkv_parti
       p.part_ml[row * 2 + 1] = ls;
     }
   }
+  finish_split<T, kD>(p, b, hk, rows, tid, kThreadsDecode);
 }
 
 // ---- 16-bit inputs: the same pass on the warp-level tensor-core path ------------------------------
@@ -487,60 +550,18 @@ __global__ void __launch_bounds__(kMmaWarps * 32, kNT == 1 ? 3 : 2) splitkv_part
       p.part_ml[row * 2 + 1] = ls;
     }
   }
-}
-
-// one warp per (b, h, query row): merge the splits
-template <typename T, int kD>
-__global__ void __launch_bounds__(256) splitkv_combine_kernel(const SplitKvParams p) {
-  const int64_t row = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  const int64_t total = (int64_t)p.B * p.Hq * p.Sq;
-  if (row >= total) return;
-  const float* ml = p.part_ml + row * p.nsplit * 2;
-  float m = -INFINITY;
-  for (int s = 0; s < p.nsplit; ++s) m = fmaxf(m, ml[s * 2]);
-  const float m_use = (m == -INFINITY) ? 0.f : m;
-  float l = 0.f;
-  constexpr int kPerLane = kD / 32;
-  float o[kPerLane];
-#pragma unroll
-  for (int i = 0; i < kPerLane; ++i) o[i] = 0.f;
-  for (int s = 0; s < p.nsplit; ++s) {
-    const float ms = ml[s * 2];
-    if (ms == -INFINITY) continue;   // this split saw no visible key
-    const float w = exp2f(ms - m_use);
-    l += ml[s * 2 + 1] * w;
-    const float* po = p.part_o + (row * p.nsplit + s) * kD;
-#pragma unroll
-    for (int i = 0; i < kPerLane; ++i) o[i] = fmaf(po[lane + 32 * i], w, o[i]);
-  }
-  const int qi = (int)(row % p.Sq);
-  const int h = (int)((row / p.Sq) % p.Hq);
-  const int b = (int)(row / ((int64_t)p.Sq * p.Hq));
-  T* out = reinterpret_cast<T*>(p.out.ptr) + (int64_t)b * p.out.sb + (int64_t)h * p.out.sh + (int64_t)qi * p.out.ss;
-  const float inv = l > 0.f ? 1.f / l : 0.f;   // a row that saw no key at all: 0 with lse -inf
-#pragma unroll
-  for (int i = 0; i < kPerLane; ++i) out[lane + 32 * i] = st_f32<T>(o[i] * inv);
-  if (lane == 0) p.lse[row] = l > 0.f ? m * 0.6931471805599453f + logf(l) : -INFINITY;
+  finish_split<T, kD>(p, b, hk, rows, tid, kMmaWarps * 32);
 }
 
 template <typename T, int kD, int kR>
 cudaError_t launch_rows(const SplitKvParams& p, cudaStream_t stream) {
   splitkv_partial_kernel<T, kD, kR><<<dim3(p.nsplit, p.Hkv, p.B), kThreadsDecode, 0, stream>>>(p);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return e;
-  const int64_t rows = (int64_t)p.B * p.Hq * p.Sq;
-  splitkv_combine_kernel<T, kD><<<(unsigned)((rows * 32 + 255) / 256), 256, 0, stream>>>(p);
   return cudaGetLastError();
 }
 
 template <typename T, int kD, int kNT>
 cudaError_t launch_mma(const SplitKvParams& p, cudaStream_t stream) {
   splitkv_partial_mma_kernel<T, kD, kNT><<<dim3(p.nsplit, p.Hkv, p.B), kMmaWarps * 32, 0, stream>>>(p);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return e;
-  const int64_t rows = (int64_t)p.B * p.Hq * p.Sq;
-  splitkv_combine_kernel<T, kD><<<(unsigned)((rows * 32 + 255) / 256), 256, 0, stream>>>(p);
   return cudaGetLastError();
 }
 
@@ -562,12 +583,15 @@ cudaError_t launch_t(const SplitKvParams& p, cudaStream_t stream) {
 }  // namespace
 
 cudaError_t launch_fwd_splitkv(const SplitKvParams& p, int dtype, cudaStream_t stream, int* launches) {
-  cudaError_t e = cudaErrorInvalidValue;
+  // the per-head counters of finished splits start at zero (a memset node, not a kernel)
+  cudaError_t e = cudaMemsetAsync(p.counters, 0, sizeof(unsigned) * p.B * p.Hkv, stream);
+  if (e != cudaSuccess) return e;
+  e = cudaErrorInvalidValue;
   if (dtype == kF32) e = (p.D == 64) ? launch_t<float, 64>(p, stream) : launch_t<float, 128>(p, stream);
   else if (dtype == kBF16)
     e = (p.D == 64) ? launch_t<__nv_bfloat16, 64>(p, stream) : launch_t<__nv_bfloat16, 128>(p, stream);
   else if (dtype == kF16) e = (p.D == 64) ? launch_t<__half, 64>(p, stream) : launch_t<__half, 128>(p, stream);
-  if (e == cudaSuccess && launches) *launches += 2;
+  if (e == cudaSuccess && launches) *launches += 1;
   return e;
 }
 

@@ -3,7 +3,7 @@
     python -m torch_mojo_backend_b200.decode_bench                      # the default list of shapes
     python -m torch_mojo_backend_b200.decode_bench --shape 8,32,8,1,32768,128 --reps 3
 
-One JSON line per shape: the time of one call of ``b200fa_fwd_splitkv`` (both of its kernels),
+One JSON line per shape: the time of one call of ``b200fa_fwd_splitkv``,
 CUDA events on the launching stream after three warm-up calls, K and V larger than L2 or an L2 flush
 between calls when they are not; ``gbs`` counts the bytes of K and V once, which is what the call
 has to read; ``frac`` divides by the measured copy bandwidth when a MEASURED_PEAKS.json lies beside

@@ -126,6 +126,31 @@ def test_split_kv_entry_point_validates_before_launch():
     assert _lib.launch_count() == before
 
 
+def _splits_of(B, Hq, Hkv, Sq, Sk, D):
+    """The split count the library chose, read back from the workspace size: fp32 partial outputs
+    and (max, sum) pairs per (row, split), one counter per (batch, KV head), each 256-byte aligned."""
+    total = _lib.fwd_splitkv_workspace_bytes(B, Hq, Hkv, Sq, Sk, D)
+    al = lambda x: (x + 255) // 256 * 256
+    rows = B * Hq * Sq
+    for n in range(1, 65):
+        if al(rows * n * D * 4) + al(rows * n * 8) + al(B * Hkv * 4) == total:
+            return n
+    raise AssertionError(f"workspace of {total} bytes fits no split count")
+
+
+def test_split_count_fills_whole_waves_of_the_grid():
+    # few (batch, KV head) pairs over a long cache: one wave of 3 x 148 thread blocks, not one and a bit
+    n = _splits_of(1, 32, 8, 1, 131072, 128)
+    assert 8 * n <= 444 < 8 * (n + 8) and 131072 // n >= 256
+    # many pairs: a handful of long splits (the fixed cost per thread block outweighs a fuller last wave)
+    assert _splits_of(64, 32, 8, 1, 8192, 128) <= 8
+    # more than eight rows per KV head: two thread blocks per SM
+    n16 = _splits_of(1, 32, 2, 1, 131072, 128)
+    assert 2 * n16 <= 296
+    # a split is never shorter than 256 keys (but for the last one)
+    assert _splits_of(1, 8, 8, 1, 600, 64) <= 3 and _splits_of(2, 4, 4, 1, 200, 64) == 1
+
+
 def test_forward_kernel_shape_setter():
     assert _lib.fwd_tiles() in (0, 1, 2)
     for tiles in (1, 2, 0):

@@ -76,6 +76,26 @@ def test_cross_attention_through_sdpa_with_grad(mojo):
     assert_within("causal out", out_causal.detach().cpu(), ref_causal, TOL_16BIT, torch.bfloat16)
 
 
+def test_decode_shaped_sdpa_takes_the_split_kv_kernel_and_its_backward_matches(mojo):
+    """Two new tokens per sequence against a 3000-token cache, GQA: the forward is served by the
+    split-KV call, and the generated autograd node runs the ordinary backward kernels on its
+    out / logsumexp."""
+    g = torch.Generator().manual_seed(17)
+    q = (torch.randn(2, 8, 2, 128, generator=g) * 0.5).bfloat16()
+    k = (torch.randn(2, 2, 3000, 128, generator=g) * 0.5).bfloat16()
+    v = (torch.randn(2, 2, 3000, 128, generator=g) * 0.5).bfloat16()
+    dout = torch.randn(2, 8, 2, 128, generator=g).bfloat16()
+    ref_out, rdq, rdk, rdv = O.sdpa_backward(q, k, v, dout, False, 128 ** -0.5)
+    qm, km, vm = (t.to(mojo).requires_grad_() for t in (q, k, v))
+    before = flash_ops.CALL_COUNTERS["forward_split_kv"]
+    out = torch.nn.functional.scaled_dot_product_attention(qm, km, vm, enable_gqa=True)
+    assert flash_ops.CALL_COUNTERS["forward_split_kv"] == before + 1
+    out.backward(dout.to(mojo))
+    assert_within("out", out.detach().cpu(), ref_out, TOL_16BIT, torch.bfloat16)
+    for name, got, ref in (("dq", qm.grad, rdq), ("dk", km.grad, rdk), ("dv", vm.grad, rdv)):
+        assert_within(name, got.cpu(), ref, TOL_16BIT, torch.bfloat16)
+
+
 def test_autocast_block_runs_the_bf16_kernel(mojo):
     g = torch.Generator().manual_seed(11)
     q, k, v = (torch.randn(2, 4, 256, 64, generator=g) * 0.5 for _ in range(3))

@@ -26,6 +26,8 @@ in HBM; ``e2e`` runs the same step on HOST tensors through the package's public 
 ``F.scaled_dot_product_attention`` + ``backward`` over the whole batch), host<->device copies
 inside the timed region; ``roofline`` times the dominant kernel alone; ``cpu_baseline`` is the
 CPU oracle timed on the host cores on a bounded slice of the same workload.
+``detail`` times the forward, the backward and its kernels on their own and, on one GPU, the
+split-KV decode call on a 32k-token cache with its HBM roofline (outside the timed region).
 """
 
 from __future__ import annotations
